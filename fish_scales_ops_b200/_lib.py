@@ -1,0 +1,95 @@
+"""ctypes binding of the C ABI in ``include/fso_b200.h``.
+
+There is no other implementation behind these calls: when ``libfso_b200.so`` is missing or a call fails, the
+caller gets an exception, never a slower path.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _build
+
+_c_i64 = ctypes.c_int64
+_c_p = ctypes.c_void_p
+
+# Every entry point of include/fso_b200.h with its argument types (the return type is int unless stated).
+SIGNATURES = {
+    "fso_b200_version": [],
+    "fso_b200_last_error": [],
+    "fso_b200_device_status": [ctypes.POINTER(ctypes.c_int)],
+    "fso_quantize_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
+    "fso_requant_bs128_to_mx": [_c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
+    "fso_pack_ue8m0": [_c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p],
+    "fso_gemm_mxfp8_ws_bytes": [_c_i64, _c_i64, _c_i64, ctypes.POINTER(_c_i64)],
+    "fso_gemm_mxfp8": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_i64, _c_p],
+    "fso_moe_plan_make": [_c_i64, _c_i64, _c_i64, _c_p],
+    "fso_moe_route": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_p],
+    "fso_moe_gather_quant": [_c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p],
+    "fso_moe_fc1_swiglu": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p,
+                           _c_p],
+    "fso_moe_fc2": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p],
+    "fso_moe_combine": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
+}
+
+
+class MoePlan(ctypes.Structure):
+    _fields_ = [("pairs", _c_i64), ("num_blocks", _c_i64), ("rows", _c_i64), ("route_scratch_bytes", _c_i64)]
+
+
+_LIB = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def lib():
+    """The loaded library; raises when it has not been built (``__graft_entry__.build()`` or
+    ``fish_scales_ops_b200.build()`` builds it)."""
+    global _LIB
+    if _LIB is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"fish_scales_ops_b200: the CUDA library {path} is missing; build it with "
+                f"fish_scales_ops_b200.build() (nvcc, sm_100a). There is no fallback implementation.")
+        handle = ctypes.CDLL(path)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_char_p if name == "fso_b200_last_error" else ctypes.c_int
+        _LIB = handle
+    return _LIB
+
+
+def last_error() -> str:
+    msg = lib().fso_b200_last_error()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(rc: int, op: str) -> None:
+    """Turn a C-ABI return code into the exception the reference raises for the same condition."""
+    if rc == 0:
+        return
+    msg = f"{op}: {last_error()}"
+    if rc == -1:
+        raise ValueError(msg)
+    if rc == -2:
+        raise NotImplementedError(msg)
+    raise RuntimeError(f"{msg} (code {rc})")
+
+
+def ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def device_status() -> int:
+    """The device-side status word of the current device (0 = no kernel wait ever ran out); synchronizes."""
+    v = ctypes.c_int(0)
+    check(lib().fso_b200_device_status(ctypes.byref(v)), "fso_b200_device_status")
+    return v.value

@@ -1,0 +1,158 @@
+"""Tensor-level wrappers of the C ABI: they allocate the outputs with the torch caching allocator on the current
+stream and call the library with raw pointers. No wrapper synchronizes or reads a tensor's values, so every call is
+capturable into a CUDA graph after one eager call of the same shape.
+
+These are the counterparts of the reference's raw ops (csrc/gemm/bindings.cpp:189-360) for the sm_100 path:
+``quantize_1x32_packed``, ``linear_mxfp8_raw``, ``moe_build_routing_compact``,
+``quantize_1x32_grouped_gather_out``, ``linear_mxfp8_grouped_compact[_swiglu]`` and ``moe_combine``.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import MoePlan, check, lib, ptr, stream_ptr
+
+FP8 = torch.float8_e4m3fn
+
+
+def _align(v: int, a: int) -> int:
+    return (v + a - 1) // a * a
+
+
+def sf_words(rows: int, k: int) -> int:
+    """int32 words of the scale tensor of a [rows, k] MXFP8 tensor (padded rows included)."""
+    return _align(rows, 128) * (k // 128)
+
+
+def quantize_1x32_fp8(x: torch.Tensor, interleave_i: int = 0):
+    """bf16 [M, K] -> (float8_e4m3fn [M, K], int32 [align(M,128) * K/128]); python/fish_scales_ops/gemm/mxfp8.py:191-213."""
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
+        raise ValueError(f"quantize_1x32_fp8: x must be a CUDA bf16 [M, K] tensor, got {x.dtype} {tuple(x.shape)}")
+    x = x.contiguous()
+    m, k = int(x.shape[0]), int(x.shape[1])
+    if k % 128 != 0:
+        raise ValueError(f"quantize_1x32_fp8: K = {k} is not a multiple of 128")
+    with torch.cuda.device(x.device):
+        xq = torch.empty((m, k), dtype=FP8, device=x.device)
+        sf = torch.empty((sf_words(m, k),), dtype=torch.int32, device=x.device)
+        if m > 0:
+            check(lib().fso_quantize_1x32(ptr(x), ptr(xq), ptr(sf), m, k, int(interleave_i), stream_ptr()),
+                  "fso_quantize_1x32")
+    return xq, sf
+
+
+def quantize_experts_1x32_fp8(w: torch.Tensor, interleave: bool):
+    """bf16 [E, N, K] -> (float8_e4m3fn [E, N, K], int32 [E, N * K/128]), one atom slab per expert
+    (python/fish_scales_ops/gemm/mxfp8.py:1511-1582). With ``interleave`` the rows of every expert are re-ordered
+    [gate; up] -> [g0, u0, g1, u1, ...] on the way."""
+    e, n, k = (int(v) for v in w.shape)
+    if n % 128 != 0 or k % 128 != 0:
+        raise ValueError(f"quantize_experts_1x32_fp8: N = {n} and K = {k} must be multiples of 128")
+    q, s = quantize_1x32_fp8(w.reshape(e * n, k), interleave_i=n // 2 if interleave else 0)
+    return q.view(e, n, k), s.view(e, n * (k // 128))
+
+
+def requant_block_fp8(wq: torch.Tensor, scale: torch.Tensor, interleave_i: int = 0):
+    """Block-FP8 [N, K] + fp32 [N/128, K/128] -> MXFP8 (python/fish_scales_ops/dense/__init__.py:422-462).
+    ``interleave_i``: the rows are stacked [2*I, K] experts re-ordered [gate; up] -> [g0, u0, ...] on the way."""
+    n, k = int(wq.shape[0]), int(wq.shape[1])
+    wq = wq.contiguous()
+    scale = scale.contiguous()
+    with torch.cuda.device(wq.device):
+        q = torch.empty((n, k), dtype=FP8, device=wq.device)
+        sf = torch.empty((sf_words(n, k),), dtype=torch.int32, device=wq.device)
+        check(lib().fso_requant_bs128_to_mx(ptr(wq), ptr(scale), ptr(q), ptr(sf), n, k, int(interleave_i), stream_ptr()),
+              "fso_requant_bs128_to_mx")
+    return q, sf
+
+
+def pack_ue8m0(sf_u8: torch.Tensor, interleave: bool = False) -> torch.Tensor:
+    """uint8 [G, N, K/32] -> int32 [G, align(N,128) * K/128] (python/fish_scales_ops/gemm/mxfp8.py:718-768)."""
+    if sf_u8.dtype != torch.uint8 or sf_u8.dim() != 3 or int(sf_u8.shape[2]) % 4 != 0:
+        raise ValueError(f"pack_ue8m0: sf must be uint8 [G, N, K/32] with K % 128 == 0, got {sf_u8.dtype} "
+                         f"{list(sf_u8.shape)}")
+    s = sf_u8.contiguous()
+    g, n, k = int(s.shape[0]), int(s.shape[1]), int(s.shape[2]) * 32
+    with torch.cuda.device(s.device):
+        out = torch.empty((g, sf_words(n, k)), dtype=torch.int32, device=s.device)
+        check(lib().fso_pack_ue8m0(ptr(s), ptr(out), g, n, k, n // 2 if interleave else 0, stream_ptr()),
+              "fso_pack_ue8m0")
+    return out
+
+
+def gemm_ws_bytes(m: int, n: int, k: int) -> int:
+    v = ctypes.c_int64(0)
+    check(lib().fso_gemm_mxfp8_ws_bytes(m, n, k, ctypes.byref(v)), "fso_gemm_mxfp8_ws_bytes")
+    return int(v.value)
+
+
+def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.Tensor) -> torch.Tensor:
+    """bf16 [M, N] = xq [M, K] @ w [N, K]^T over MXFP8 operands (python/fish_scales_ops/gemm/mxfp8.py:90-188)."""
+    m, k = int(xq.shape[0]), int(xq.shape[1])
+    n = int(w.shape[0])
+    with torch.cuda.device(xq.device):
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
+        if m == 0:
+            return out
+        ws_bytes = gemm_ws_bytes(m, n, k)
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=xq.device) if ws_bytes > 0 else None
+        check(lib().fso_gemm_mxfp8(ptr(xq), ptr(sx), ptr(w), ptr(sw), ptr(out), m, n, k, ptr(ws), ws_bytes,
+                                   stream_ptr()), "fso_gemm_mxfp8")
+    return out
+
+
+def moe_plan(tokens: int, topk: int, num_experts: int) -> MoePlan:
+    p = MoePlan()
+    check(lib().fso_moe_plan_make(tokens, topk, num_experts, ctypes.byref(p)), "fso_moe_plan_make")
+    return p
+
+
+def moe_route(ids: torch.Tensor, num_experts: int, plan: MoePlan):
+    """ids int32 [T, topk] -> (masked_m [E], blk0 [E+1], slot_of_flat [T*topk], blk_expert [num_blocks])."""
+    t, topk = int(ids.shape[0]), int(ids.shape[1])
+    dev = ids.device
+    with torch.cuda.device(dev):
+        masked_m = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+        blk0 = torch.empty((num_experts + 1,), dtype=torch.int32, device=dev)
+        slot = torch.empty((t * topk,), dtype=torch.int32, device=dev)
+        blk_expert = torch.empty((int(plan.num_blocks),), dtype=torch.int32, device=dev)
+        sb = int(plan.route_scratch_bytes)
+        scratch = torch.empty((sb,), dtype=torch.uint8, device=dev) if sb > 0 else None
+        check(lib().fso_moe_route(ptr(ids), t, topk, num_experts, int(plan.num_blocks), ptr(masked_m), ptr(blk0),
+                                  ptr(slot), ptr(blk_expert), ptr(scratch), sb, stream_ptr()), "fso_moe_route")
+    return masked_m, blk0, slot, blk_expert
+
+
+def moe_gather_quant(hidden: torch.Tensor, slot: torch.Tensor, topk: int, hq: torch.Tensor, sh: torch.Tensor):
+    t, h = int(hidden.shape[0]), int(hidden.shape[1])
+    with torch.cuda.device(hidden.device):
+        check(lib().fso_moe_gather_quant(ptr(hidden), ptr(slot), t, topk, h, int(hq.shape[0]), ptr(hq), ptr(sh),
+                                         stream_ptr()), "fso_moe_gather_quant")
+
+
+def moe_fc1_swiglu(hq, sh, w13, sw13, blk0, blk_expert, dq, sd):
+    e, two_i, h = (int(v) for v in w13.shape)
+    with torch.cuda.device(hq.device):
+        check(lib().fso_moe_fc1_swiglu(ptr(hq), ptr(sh), ptr(w13), ptr(sw13), ptr(blk0), ptr(blk_expert), e, h,
+                                       two_i // 2, int(blk_expert.shape[0]), int(hq.shape[0]), ptr(dq), ptr(sd),
+                                       stream_ptr()), "fso_moe_fc1_swiglu")
+
+
+def moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn):
+    e, h, inter = (int(v) for v in w2.shape)
+    with torch.cuda.device(dq.device):
+        check(lib().fso_moe_fc2(ptr(dq), ptr(sd), ptr(w2), ptr(sw2), ptr(blk0), ptr(blk_expert), e, h, inter,
+                                int(blk_expert.shape[0]), int(dq.shape[0]), ptr(dn), stream_ptr()), "fso_moe_fc2")
+
+
+def moe_combine(dn, slot, topk_w, bias, bias_scale, out):
+    t, h = int(out.shape[0]), int(out.shape[1])
+    topk = int(topk_w.shape[1])
+    with torch.cuda.device(dn.device):
+        check(lib().fso_moe_combine(ptr(dn), ptr(slot), ptr(topk_w), ptr(bias), ptr(bias_scale), ptr(out), t, topk, h,
+                                    stream_ptr()), "fso_moe_combine")
+
+
+def device_status() -> int:
+    return _lib.device_status()

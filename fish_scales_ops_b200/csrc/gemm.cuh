@@ -1,0 +1,449 @@
+// MXFP8 block-scaled GEMM for sm_100a: tcgen05.mma kind::mxf8f6f4.block_scale, operands fed by TMA into a
+// multi-stage shared-memory ring, UE8M0 scale factors copied shared -> tensor memory per K block, fp32
+// accumulators in tensor memory, persistent CTAs (one per SM) with a static tile schedule.
+//
+// One kernel template serves four uses:
+//   * dense, normal orientation   activation rows on MMA-M (128), weight rows on MMA-N (128 / 256)
+//   * dense, swapped orientation  weight rows on MMA-M (128), the (<= 64) activation rows on MMA-N (16 / 32 / 64):
+//                                 the weight stream is what the decode-sized problem costs
+//   * split-K of either           fp32 partials to a workspace, summed in slice order by a second kernel
+//   * grouped (MoE)               A rows are the 128-row blocks of the compact activation, the weight of each block
+//                                 is picked through the block -> expert table; optional fused SiLU(gate)*up
+//                                 requantize epilogue (FC1) that writes e4m3 + scale words directly
+//
+// Warp roles: warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one lane),
+// warps 4.. = epilogue (warp w reads the 32-lane quarter w % 4 of the accumulator).
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "quant.cuh"
+
+namespace fso {
+
+enum : int { EPI_BF16 = 0, EPI_PARTIAL = 1, EPI_SWIGLU = 2 };
+
+struct GemmParams {
+    const uint8_t* sfa;        // scale words of the operand on MMA-M
+    const uint8_t* sfb;        // scale words of the operand on MMA-N
+    void* out;                 // bf16 [M, N]; EPI_SWIGLU: e4m3 [rows, I]
+    uint32_t* out_sf;          // EPI_SWIGLU: scale words of the [rows, I] output
+    float* ws;                 // EPI_PARTIAL: fp32 [splits, M, N]
+    const int32_t* blk0;       // grouped: blk0[num_experts] = blocks in use
+    const int32_t* blk_expert; // grouped: expert of each 128-row block
+    int rows_a;                // valid rows of the MMA-M operand
+    int rows_b;                // valid rows of the MMA-N operand (per expert when grouped)
+    int kb_total;              // K / 128
+    int kb_per_split;
+    int splits;
+    int tiles_a;               // 128-row tiles of the MMA-M operand (grouped: bound on the blocks)
+    int tiles_b;               // BN-row tiles of the MMA-N operand
+    int ldo;                   // leading dimension of out / ws rows, in elements
+    int num_experts;
+    int group_a;               // raster: tiles of A walked together before B advances
+    int64_t out_rows;          // rows of the output (row stride of one split's partial = out_rows * ldo)
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int kBM = 128;
+    static constexpr int kBK = 128;                                   // bytes == elements along K per stage
+    static constexpr int kEpiWarps = BN >= 128 ? 8 : 4;
+    static constexpr int kThreads = 128 + 32 * kEpiWarps;
+    static constexpr int kAccStages = BN == 256 ? 1 : 2;
+    static constexpr int kABytes = kBM * kBK;
+    static constexpr int kBBytes = BN * kBK;
+    static constexpr int kSfaBytes = 512;
+    static constexpr int kSfbAtoms = BN > 128 ? BN / 128 : 1;
+    static constexpr int kSfbBytes = 512 * kSfbAtoms;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - 512 /*barriers*/;
+    static constexpr int kStagesMax = kSmemBudget / kStageBytes;
+    static constexpr int kStages = kStagesMax > 12 ? 12 : kStagesMax;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+    // tensor-memory columns: accumulators first, then two alternating scale-factor buffers
+    static constexpr int kAccCols = kAccStages * BN;
+    static constexpr int kSfaCols = 4;
+    static constexpr int kSfbCols = 4 * kSfbAtoms;
+    static constexpr int kSfBufCols = kSfaCols + kSfbCols;
+    static constexpr int kColsUsed = kAccCols + 2 * kSfBufCols;
+    static constexpr int kTmemCols = kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128
+        : kColsUsed <= 256 ? 256 : 512;
+    static_assert(kColsUsed <= 512, "tensor memory budget");
+    static_assert(kStages >= 3, "pipeline depth");
+    static_assert(kSmemBytes > 116 * 1024, "one CTA per SM is assumed by the tensor-memory allocation");
+};
+
+struct TileCoord {
+    int a_tile;     // 128-row tile of the MMA-M operand (grouped: block index)
+    int b_tile;     // BN-row tile of the MMA-N operand
+    int split;
+    int expert;     // grouped: expert of the block; otherwise 0
+};
+
+// Static schedule: work item t of (tiles_a_used * tiles_b * splits). A tiles advance fastest inside a group of
+// `group_a`, then B tiles, then the next group; the split index is the slowest inside a tile pair.
+template <bool kGrouped>
+__device__ __forceinline__ bool decode_tile(GemmParams const& p, int t, int tiles_a_used, TileCoord& c)
+{
+    int const per_split = tiles_a_used * p.tiles_b;
+    if (t >= per_split * p.splits) return false;
+    c.split = t / per_split;
+    int const r = t - c.split * per_split;
+    int const group_span = p.group_a * p.tiles_b;
+    int const g = r / group_span;
+    int const first_a = g * p.group_a;
+    int const gsz = min(p.group_a, tiles_a_used - first_a);
+    int const in_g = r - g * group_span;
+    c.b_tile = in_g / gsz;
+    c.a_tile = first_a + (in_g - c.b_tile * gsz);
+    c.expert = 0;
+    if constexpr (kGrouped) c.expert = p.blk_expert[c.a_tile];
+    return true;
+}
+
+__device__ __forceinline__ void record_abort(int code, volatile int* abort_flag)
+{
+    atomicCAS(&g_dev_status, 0, code);
+    *abort_flag = 1;
+}
+
+// Bounded wait that also leaves when another role of this CTA has already given up.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    long long const t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) return false;
+    }
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u)
+{
+    // silu(g) = g * sigmoid(g) = 0.5 * g * (1 + tanh(0.5 * g)), with the hardware tanh approximation
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * g));
+    return (0.5f * g) * (1.f + t) * u;
+}
+
+template <int BN, int EPI, bool kSwap, bool kGrouped>
+__global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
+gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+    const GemmParams p)
+{
+    using C = GemmCfg<BN>;
+    constexpr int S = C::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint32_t const raw = smem_u32(smem_raw);
+    uint32_t const base = (raw + 1023u) & ~1023u;
+    uint8_t* const gbase = smem_raw + (base - raw);
+
+    uint32_t const sA = base;
+    uint32_t const sB = sA + S * C::kABytes;
+    uint32_t const sSfa = sB + S * C::kBBytes;
+    uint32_t const sSfb = sSfa + S * C::kSfaBytes;
+    uint32_t const bars = sSfb + S * C::kSfbBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * S + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * S + 2 + a); };
+    uint32_t const misc_off = static_cast<uint32_t>(S) * C::kStageBytes + 8u * (2 * S + 4);
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gbase + misc_off);
+    volatile int* const abort_flag = reinterpret_cast<volatile int*>(gbase + misc_off + 4);
+
+    int const warp = threadIdx.x >> 5;
+    int const lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), C::kEpiWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t const tmem_base = *tmem_slot;
+
+    int tiles_a_used = p.tiles_a;
+    if constexpr (kGrouped) tiles_a_used = min(p.tiles_a, p.blk0[p.num_experts]);
+    int const rows_b_pad = (p.rows_b + 127) & ~127;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            TileCoord c;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && decode_tile<kGrouped>(p, t, tiles_a_used, c); t += gridDim.x) {
+                int const kb0 = c.split * p.kb_per_split;
+                int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                int const a_row0 = c.a_tile * C::kBM;
+                int const b_row0 = c.b_tile * BN;
+                int const b_coord = kGrouped ? c.expert * p.rows_b + b_row0 : b_row0;
+                const uint8_t* sfb_base = p.sfb
+                    + (kGrouped ? static_cast<int64_t>(c.expert) * (rows_b_pad / 128) * p.kb_total * 512 : 0);
+                int sfb_atoms = 0;
+                for (int j = 0; j < C::kSfbAtoms; ++j)
+                    if (b_row0 + j * 128 < rows_b_pad) ++sfb_atoms;
+                uint32_t const bytes = C::kABytes + C::kBBytes + C::kSfaBytes + 512u * sfb_atoms;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!wait_or_abort(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        record_abort(FSO_DEV_WAIT_PRODUCER, abort_flag);
+                        ok = false;
+                        break;
+                    }
+                    uint32_t const fb = full_bar(stage);
+                    mbar_expect_tx(fb, bytes);
+                    tma_load_2d(sA + stage * C::kABytes, &tm_a, fb, kb * C::kBK, a_row0);
+                    tma_load_2d(sB + stage * C::kBBytes, &tm_b, fb, kb * C::kBK, b_coord);
+                    bulk_load(sSfa + stage * C::kSfaBytes,
+                        p.sfa + (static_cast<int64_t>(a_row0 / 128) * p.kb_total + kb) * 512, 512, fb);
+                    for (int j = 0; j < sfb_atoms; ++j)
+                        bulk_load(sSfb + stage * C::kSfbBytes + j * 512,
+                            sfb_base + (static_cast<int64_t>(b_row0 / 128 + j) * p.kb_total + kb) * 512, 512, fb);
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            int sfbuf = 0;
+            constexpr uint32_t idesc = make_idesc_mxf8(BN);
+            TileCoord c;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && decode_tile<kGrouped>(p, t, tiles_a_used, c); t += gridDim.x) {
+                int const kb0 = c.split * p.kb_per_split;
+                int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                if (!wait_or_abort(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+                    record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
+                    break;
+                }
+                tc_fence_after();
+                uint32_t const d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                uint32_t const sfb_col_off = BN < 128 ? static_cast<uint32_t>(((c.b_tile * BN) & 127) >> 5) : 0u;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!wait_or_abort(full_bar(stage), phase, abort_flag)) {
+                        record_abort(FSO_DEV_WAIT_MMA_FULL, abort_flag);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint32_t const sf_col = tmem_base + C::kAccCols + sfbuf * C::kSfBufCols;
+                    tc_cp_32x128b_warpx4(sf_col, make_desc_sf(sSfa + stage * C::kSfaBytes));
+#pragma unroll
+                    for (int j = 0; j < C::kSfbAtoms; ++j)
+                        tc_cp_32x128b_warpx4(sf_col + C::kSfaCols + 4 * j,
+                            make_desc_sf(sSfb + stage * C::kSfbBytes + j * 512));
+                    uint64_t const adesc = make_desc_sw128(sA + stage * C::kABytes);
+                    uint64_t const bdesc = make_desc_sw128(sB + stage * C::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_mxf8(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc | sf_id_bits(k), sf_col,
+                            sf_col + C::kSfaCols + sfb_col_off, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty_bar(stage));
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    sfbuf ^= 1;
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(acc));
+                if (++acc == C::kAccStages) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------------------------ epilogue
+        int const ew = warp - 4;
+        int const quarter = warp & 3;
+        int const half = ew >> 2;
+        constexpr int kColsPerWarp = BN / (C::kEpiWarps / 4);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        TileCoord c;
+        for (int t = blockIdx.x; decode_tile<kGrouped>(p, t, tiles_a_used, c); t += gridDim.x) {
+            if (!wait_or_abort(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (lane == 0) record_abort(FSO_DEV_WAIT_EPILOGUE, abort_flag);
+                break;
+            }
+            tc_fence_after();
+            uint32_t const t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16)
+                + static_cast<uint32_t>(acc * BN);
+            int const a_row = c.a_tile * C::kBM + quarter * 32 + lane;   // this thread's row of the MMA-M operand
+            int const b_row0 = c.b_tile * BN;
+
+            if constexpr (EPI == EPI_SWIGLU) {
+                // interleaved (gate, up) columns -> 64 outputs per warp = two 1x32 blocks per row
+                int const inter = p.ldo;
+                uint8_t* const drow = static_cast<uint8_t*>(p.out) + static_cast<int64_t>(a_row) * inter
+                    + c.b_tile * (BN / 2) + half * (kColsPerWarp / 2);
+                uint32_t bytes2 = 0;
+#pragma unroll
+                for (int blk = 0; blk < kColsPerWarp / 64; ++blk) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(t_row + half * kColsPerWarp + blk * 64, r0);
+                    tmem_ld_32x32(t_row + half * kColsPerWarp + blk * 64 + 32, r1);
+                    tmem_ld_wait();
+                    float h[32];
+                    float amax = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        h[j] = silu_mul(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                        h[16 + j] = silu_mul(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                        amax = fmaxf(amax, fmaxf(fabsf(h[j]), fabsf(h[16 + j])));
+                    }
+                    amax = fmaxf(amax, 1e-10f);
+                    float qs;
+                    uint32_t const byte = e8m0_from_amax(amax, qs);
+                    bytes2 |= byte << (8 * blk);
+                    uint4 o0, o1;
+                    o0.x = fp8x4(__fmul_rn(h[0], qs), __fmul_rn(h[1], qs), __fmul_rn(h[2], qs), __fmul_rn(h[3], qs));
+                    o0.y = fp8x4(__fmul_rn(h[4], qs), __fmul_rn(h[5], qs), __fmul_rn(h[6], qs), __fmul_rn(h[7], qs));
+                    o0.z = fp8x4(__fmul_rn(h[8], qs), __fmul_rn(h[9], qs), __fmul_rn(h[10], qs), __fmul_rn(h[11], qs));
+                    o0.w = fp8x4(__fmul_rn(h[12], qs), __fmul_rn(h[13], qs), __fmul_rn(h[14], qs), __fmul_rn(h[15], qs));
+                    o1.x = fp8x4(__fmul_rn(h[16], qs), __fmul_rn(h[17], qs), __fmul_rn(h[18], qs), __fmul_rn(h[19], qs));
+                    o1.y = fp8x4(__fmul_rn(h[20], qs), __fmul_rn(h[21], qs), __fmul_rn(h[22], qs), __fmul_rn(h[23], qs));
+                    o1.z = fp8x4(__fmul_rn(h[24], qs), __fmul_rn(h[25], qs), __fmul_rn(h[26], qs), __fmul_rn(h[27], qs));
+                    o1.w = fp8x4(__fmul_rn(h[28], qs), __fmul_rn(h[29], qs), __fmul_rn(h[30], qs), __fmul_rn(h[31], qs));
+                    if (a_row < p.out_rows) {
+                        uint4* dst = reinterpret_cast<uint4*>(drow + blk * 32);
+                        dst[0] = o0;
+                        dst[1] = o1;
+                    }
+                }
+                if (a_row < p.out_rows) {
+                    // this warp owns bytes [2*half, 2*half+2) of the row's scale word for K block b_tile of the output
+                    uint8_t* const w = reinterpret_cast<uint8_t*>(p.out_sf)
+                        + sf_word_index(a_row, c.b_tile, inter / 128) * 4 + half * 2;
+                    *reinterpret_cast<uint16_t*>(w) = static_cast<uint16_t>(bytes2);
+                }
+            } else if constexpr (!kSwap) {
+                // row = output row, columns = output columns
+#pragma unroll 1
+                for (int c0 = half * kColsPerWarp; c0 < (half + 1) * kColsPerWarp; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + c0, r);
+                    tmem_ld_wait();
+                    int const col = b_row0 + c0;
+                    if (a_row < p.rows_a && col < p.rows_b) {
+                        if constexpr (EPI == EPI_BF16) {
+                            uint4* dst = reinterpret_cast<uint4*>(
+                                static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(a_row) * p.ldo + col);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+                                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                dst[v] = o;
+                            }
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>(p.ws + static_cast<int64_t>(c.split) * p.out_rows * p.ldo
+                                + static_cast<int64_t>(a_row) * p.ldo + col);
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                dst[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        }
+                    }
+                }
+            } else {
+                // swapped: this thread's row is an output COLUMN (a weight row), tensor-memory columns are tokens
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(t_row + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        int const m = b_row0 + c0 + j;
+                        if (m < p.rows_b && a_row < p.rows_a) {
+                            if constexpr (EPI == EPI_BF16)
+                                static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row]
+                                    = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            else
+                                p.ws[static_cast<int64_t>(c.split) * p.out_rows * p.ldo
+                                    + static_cast<int64_t>(m) * p.ldo + a_row] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == C::kAccStages) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out somewhere: give copies that may still be in flight time to land before the CTA leaves
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// Sums the split-K partials in slice order and rounds once to bf16. n % 4 == 0.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float4* __restrict__ ws, uint2* __restrict__ out,
+    int64_t quads, int splits)
+{
+    int64_t const i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= quads) return;
+    float4 acc = ws[i];
+    for (int s = 1; s < splits; ++s) {
+        float4 const v = ws[static_cast<int64_t>(s) * quads + i];
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc.x, acc.y);
+    o.y = pack_bf16x2(acc.z, acc.w);
+    out[i] = o;
+}
+
+}  // namespace fso

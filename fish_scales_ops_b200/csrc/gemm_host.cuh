@@ -1,0 +1,251 @@
+// Host side of the GEMM family: tensor-map encoding, the shape -> (orientation, tile, split) picker and launchers.
+#pragma once
+
+#include <atomic>
+#include <mutex>
+
+#include "gemm.cuh"
+
+namespace fso {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess
+            && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Tensor map of a row-major byte matrix [rows, k] read in boxes of 128 bytes x box_rows with the 128-byte swizzle.
+inline int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return FSO_ERR_UNSUPPORTED;
+    }
+    cuuint64_t const dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    cuuint64_t const strides[1] = {static_cast<cuuint64_t>(k)};
+    cuuint32_t const box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t const estr[2] = {1u, 1u};
+    CUresult const r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows %lld, k %lld, box %d)", static_cast<int>(r),
+            static_cast<long long>(rows), static_cast<long long>(k), box_rows);
+        return FSO_ERR_INTERNAL;
+    }
+    return 0;
+}
+
+// The route one dense shape takes. Pure host arithmetic on (M, N, K, SMs).
+struct DensePlan {
+    bool swap;      // weight rows on MMA-M, activation rows on MMA-N
+    int bn;         // MMA-N tile
+    int splits;
+    int kb_per_split;
+    int tiles_a, tiles_b;
+    int group_a;
+    int64_t ws_bytes;
+};
+
+// Fraction of the (persistent, one CTA per SM) grid kept busy by `items` equal work items.
+inline double wave_efficiency(int64_t items, int sms)
+{
+    int64_t const rounds = (items + sms - 1) / sms;
+    return static_cast<double>(items) / static_cast<double>(rounds * sms);
+}
+
+inline void pick_splits(int64_t tiles, int kb, int sms, int min_kb, int* splits, int* kb_per)
+{
+    int best_s = 1;
+    double best = wave_efficiency(tiles, sms);
+    if (tiles < sms) {
+        for (int s = 2; s <= 16; ++s) {
+            int const per = (kb + s - 1) / s;
+            if (per < min_kb) break;
+            int const real = (kb + per - 1) / per;
+            if (real != s) continue;
+            double const e = wave_efficiency(tiles * s, sms) * (static_cast<double>(kb) / (per * s));
+            if (e > best + 0.02) {
+                best = e;
+                best_s = s;
+            }
+        }
+    }
+    *splits = best_s;
+    *kb_per = (kb + best_s - 1) / best_s;
+}
+
+inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
+{
+    DensePlan p{};
+    int const kb = static_cast<int>(k / 128);
+    if (m <= 64) {
+        p.swap = true;
+        p.bn = m <= 16 ? 16 : m <= 32 ? 32 : 64;
+        p.tiles_a = static_cast<int>(n / 128);
+        p.tiles_b = 1;
+        p.group_a = p.tiles_a;
+        pick_splits(p.tiles_a, kb, sms, 4, &p.splits, &p.kb_per_split);
+    } else {
+        p.swap = false;
+        int const tiles_m = static_cast<int>((m + 127) / 128);
+        p.bn = (n % 256 == 0 && static_cast<int64_t>(tiles_m) * (n / 256) >= sms / 2) ? 256 : 128;
+        p.tiles_a = tiles_m;
+        p.tiles_b = static_cast<int>((n + p.bn - 1) / p.bn);
+        p.group_a = tiles_m < 16 ? tiles_m : 16;
+        pick_splits(static_cast<int64_t>(p.tiles_a) * p.tiles_b, kb, sms, 8, &p.splits, &p.kb_per_split);
+    }
+    p.ws_bytes = p.splits > 1 ? static_cast<int64_t>(p.splits) * m * n * 4 : 0;
+    return p;
+}
+
+template <typename Kernel>
+inline int ensure_smem_attr(Kernel kernel, int smem_bytes, std::atomic<uint64_t>& done_mask)
+{
+    int const dev = current_device();
+    uint64_t const bit = 1ull << (dev & 63);
+    if ((done_mask.load(std::memory_order_acquire) & bit) == 0) {
+        FSO_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        done_mask.fetch_or(bit, std::memory_order_release);
+    }
+    return 0;
+}
+
+template <int BN, int EPI, bool kSwap, bool kGrouped>
+inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int grid,
+    cudaStream_t stream)
+{
+    using C = GemmCfg<BN>;
+    static std::atomic<uint64_t> done{0};
+    auto kernel = gemm_mxf8_kernel<BN, EPI, kSwap, kGrouped>;
+    int const rc = ensure_smem_attr(kernel, C::kSmemBytes, done);
+    if (rc != 0) return rc;
+    kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ta, tb, p);
+    return launch_status("gemm_mxf8_kernel");
+}
+
+// D[M, N] = A[M, K] * W[N, K]^T.
+inline int launch_dense(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
+    int64_t k, void* ws, int64_t ws_bytes, cudaStream_t stream)
+{
+    int const sms = sm_count();
+    DensePlan const pl = plan_dense(m, n, k, sms);
+    if (pl.ws_bytes > 0 && (ws == nullptr || ws_bytes < pl.ws_bytes)) {
+        set_error("fso_gemm_mxfp8: this shape takes the split-K route and needs a workspace of %lld bytes "
+                  "(fso_gemm_mxfp8_ws_bytes), got %lld", static_cast<long long>(pl.ws_bytes),
+            static_cast<long long>(ws_bytes));
+        return FSO_ERR_INVALID;
+    }
+    CUtensorMap ta, tb;
+    GemmParams p{};
+    p.kb_total = static_cast<int>(k / 128);
+    p.kb_per_split = pl.kb_per_split;
+    p.splits = pl.splits;
+    p.tiles_a = pl.tiles_a;
+    p.tiles_b = pl.tiles_b;
+    p.group_a = pl.group_a;
+    p.ldo = static_cast<int>(n);
+    p.out = d;
+    p.ws = static_cast<float*>(ws);
+    p.out_rows = m;
+    int rc;
+    if (pl.swap) {
+        if ((rc = make_operand_map(&ta, w, n, k, 128)) != 0) return rc;
+        if ((rc = make_operand_map(&tb, a, m, k, pl.bn)) != 0) return rc;
+        p.sfa = static_cast<const uint8_t*>(sfw);
+        p.sfb = static_cast<const uint8_t*>(sfa);
+        p.rows_a = static_cast<int>(n);
+        p.rows_b = static_cast<int>(m);
+    } else {
+        if ((rc = make_operand_map(&ta, a, m, k, 128)) != 0) return rc;
+        if ((rc = make_operand_map(&tb, w, n, k, pl.bn)) != 0) return rc;
+        p.sfa = static_cast<const uint8_t*>(sfa);
+        p.sfb = static_cast<const uint8_t*>(sfw);
+        p.rows_a = static_cast<int>(m);
+        p.rows_b = static_cast<int>(n);
+    }
+    int64_t const items = static_cast<int64_t>(pl.tiles_a) * pl.tiles_b * pl.splits;
+    int const grid = static_cast<int>(items < sms ? items : sms);
+    bool const partial = pl.splits > 1;
+#define FSO_DENSE_CASE(BN_, SWAP_)                                                                                 \
+    if (pl.bn == BN_ && pl.swap == SWAP_) {                                                                        \
+        rc = partial ? launch_gemm_inst<BN_, EPI_PARTIAL, SWAP_, false>(ta, tb, p, grid, stream)                   \
+                     : launch_gemm_inst<BN_, EPI_BF16, SWAP_, false>(ta, tb, p, grid, stream);                     \
+    } else
+    FSO_DENSE_CASE(16, true)
+    FSO_DENSE_CASE(32, true)
+    FSO_DENSE_CASE(64, true)
+    FSO_DENSE_CASE(128, false)
+    FSO_DENSE_CASE(256, false)
+    {
+        set_error("fso_gemm_mxfp8: no kernel for tile %d (swap %d)", pl.bn, static_cast<int>(pl.swap));
+        return FSO_ERR_INTERNAL;
+    }
+#undef FSO_DENSE_CASE
+    if (rc != 0) return rc;
+    if (partial) {
+        int64_t const quads = m * n / 4;
+        splitk_reduce_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, stream>>>(
+            static_cast<const float4*>(ws), static_cast<uint2*>(d), quads, pl.splits);
+        rc = launch_status("splitk_reduce_kernel");
+    }
+    return rc;
+}
+
+// Grouped GEMM over the compact activation: block b (rows [128b, 128b+128) of `a`) times weight[blk_expert[b]]^T.
+// weight is [E, n_w, k] contiguous, its scale words one atom slab of n_w * k/128 words per expert.
+// swiglu: n_w = 2I interleaved gate/up rows, out = e4m3 [rows, I] with scale words out_sf; otherwise out = bf16
+// [rows, n_w].
+inline int launch_grouped(const void* a, const void* sfa, const void* weight, const void* sfw, const int32_t* blk0,
+    const int32_t* blk_expert, int64_t num_experts, int64_t n_w, int64_t k, int64_t num_blocks, int64_t rows,
+    void* out, void* out_sf, bool swiglu, cudaStream_t stream)
+{
+    int const sms = sm_count();
+    int const bn = (n_w % 256 == 0) ? 256 : 128;
+    if (swiglu && bn != 256) {
+        set_error("fso_moe_fc1_swiglu: 2*I must be a multiple of 256");
+        return FSO_ERR_INVALID;
+    }
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_operand_map(&ta, a, rows, k, 128)) != 0) return rc;
+    if ((rc = make_operand_map(&tb, weight, num_experts * n_w, k, bn)) != 0) return rc;
+    GemmParams p{};
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb = static_cast<const uint8_t*>(sfw);
+    p.out = out;
+    p.out_sf = static_cast<uint32_t*>(out_sf);
+    p.blk0 = blk0;
+    p.blk_expert = blk_expert;
+    p.rows_a = static_cast<int>(rows);
+    p.rows_b = static_cast<int>(n_w);
+    p.kb_total = static_cast<int>(k / 128);
+    p.kb_per_split = p.kb_total;
+    p.splits = 1;
+    p.tiles_a = static_cast<int>(num_blocks);
+    p.tiles_b = static_cast<int>(n_w / bn);
+    p.ldo = swiglu ? static_cast<int>(n_w / 2) : static_cast<int>(n_w);
+    p.num_experts = static_cast<int>(num_experts);
+    p.group_a = 16;
+    p.out_rows = rows;
+    int64_t const items = static_cast<int64_t>(p.tiles_a) * p.tiles_b;
+    int const grid = static_cast<int>(items < sms ? items : sms);
+    if (swiglu) return launch_gemm_inst<256, EPI_SWIGLU, false, true>(ta, tb, p, grid, stream);
+    if (bn == 256) return launch_gemm_inst<256, EPI_BF16, false, true>(ta, tb, p, grid, stream);
+    return launch_gemm_inst<128, EPI_BF16, false, true>(ta, tb, p, grid, stream);
+}
+
+}  // namespace fso

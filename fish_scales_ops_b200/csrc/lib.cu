@@ -1,0 +1,264 @@
+// The one translation unit of libfso_b200.so: kernels (included headers) and the extern "C" entry points declared
+// in include/fso_b200.h. Nothing here allocates device memory or synchronizes, except fso_b200_device_status.
+#include <cstdarg>
+
+#include "common.cuh"
+
+namespace fso {
+
+static thread_local char t_error[512] = "";
+
+void set_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+}
+
+int current_device()
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev;
+}
+
+int sm_count()
+{
+    static int cached[64] = {0};
+    int const dev = current_device() & 63;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = n > 0 ? n : 1;
+    }
+    return cached[dev];
+}
+
+}  // namespace fso
+
+#include "gemm_host.cuh"
+#include "moe.cuh"
+
+using namespace fso;
+
+static inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+int fso_b200_version(void) { return 1; }
+
+const char* fso_b200_last_error(void) { return t_error; }
+
+int fso_b200_device_status(int* status)
+{
+    FSO_REQUIRE(status != nullptr, "fso_b200_device_status: status is NULL");
+    int v = 0;
+    FSO_CUDA(cudaDeviceSynchronize());
+    FSO_CUDA(cudaMemcpyFromSymbol(&v, g_dev_status, sizeof(int)));
+    if (v != 0) {
+        int const zero = 0;
+        FSO_CUDA(cudaMemcpyToSymbol(g_dev_status, &zero, sizeof(int)));
+    }
+    *status = v;
+    return 0;
+}
+
+int fso_quantize_1x32(const void* x, void* xq, void* sf, int64_t m, int64_t k, int64_t interleave_i, void* stream)
+{
+    FSO_REQUIRE(m >= 0 && k > 0 && k % 128 == 0, "fso_quantize_1x32: K = %lld must be a positive multiple of 128",
+        static_cast<long long>(k));
+    if (m == 0) return 0;
+    FSO_REQUIRE(x && xq && sf, "fso_quantize_1x32: NULL pointer");
+    FSO_REQUIRE(aligned16(x) && aligned16(xq) && (reinterpret_cast<uintptr_t>(sf) & 3u) == 0,
+        "fso_quantize_1x32: x and xq must be 16-byte aligned and sf 4-byte aligned");
+    FSO_REQUIRE(interleave_i >= 0 && (interleave_i == 0 || m % (2 * interleave_i) == 0),
+        "fso_quantize_1x32: with interleave_i = %lld the row count %lld must be a multiple of 2*I",
+        static_cast<long long>(interleave_i), static_cast<long long>(m));
+    return launch_quantize_1x32(x, xq, sf, m, k, interleave_i, as_stream(stream));
+}
+
+int fso_requant_bs128_to_mx(const void* wq, const float* s128, void* out_q, void* out_sf, int64_t n, int64_t k,
+    int64_t interleave_i, void* stream)
+{
+    FSO_REQUIRE(n > 0 && k > 0 && n % 128 == 0 && k % 128 == 0,
+        "fso_requant_bs128_to_mx: N = %lld and K = %lld must be positive multiples of 128", static_cast<long long>(n),
+        static_cast<long long>(k));
+    FSO_REQUIRE(wq && s128 && out_q && out_sf, "fso_requant_bs128_to_mx: NULL pointer");
+    FSO_REQUIRE(aligned16(wq) && aligned16(out_q) && (reinterpret_cast<uintptr_t>(out_sf) & 3u) == 0
+            && (reinterpret_cast<uintptr_t>(s128) & 3u) == 0,
+        "fso_requant_bs128_to_mx: wq and out_q must be 16-byte aligned, s128 and out_sf 4-byte aligned");
+    FSO_REQUIRE(interleave_i >= 0 && (interleave_i == 0 || (n % (2 * interleave_i) == 0 && interleave_i % 128 == 0)),
+        "fso_requant_bs128_to_mx: with interleave_i = %lld, N must be a multiple of 2*I and I a multiple of 128",
+        static_cast<long long>(interleave_i));
+    return launch_requant_bs128(wq, s128, out_q, out_sf, n, k, interleave_i, as_stream(stream));
+}
+
+int fso_pack_ue8m0(const void* sf_u8, void* out_sf, int64_t g, int64_t n, int64_t k, int64_t interleave_i,
+    void* stream)
+{
+    FSO_REQUIRE(g > 0 && n > 0 && k > 0 && k % 128 == 0, "fso_pack_ue8m0: G, N positive and K a multiple of 128");
+    FSO_REQUIRE(sf_u8 && out_sf && (reinterpret_cast<uintptr_t>(out_sf) & 3u) == 0,
+        "fso_pack_ue8m0: NULL pointer or out_sf not 4-byte aligned");
+    FSO_REQUIRE(interleave_i >= 0 && (interleave_i == 0 || n == 2 * interleave_i),
+        "fso_pack_ue8m0: with interleave_i the row count per group must be 2*I");
+    return launch_pack_ue8m0(sf_u8, out_sf, g, n, k, interleave_i, as_stream(stream));
+}
+
+static int check_gemm_shape(const char* op, int64_t m, int64_t n, int64_t k)
+{
+    FSO_REQUIRE(m >= 0 && n > 0 && k > 0, "%s: M >= 0, N > 0, K > 0 required", op);
+    FSO_REQUIRE(n % 128 == 0 && k % 128 == 0, "%s: N = %lld and K = %lld must be multiples of 128", op,
+        static_cast<long long>(n), static_cast<long long>(k));
+    FSO_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "%s: dimension too large", op);
+    return 0;
+}
+
+int fso_gemm_mxfp8_ws_bytes(int64_t m, int64_t n, int64_t k, int64_t* bytes)
+{
+    FSO_REQUIRE(bytes != nullptr, "fso_gemm_mxfp8_ws_bytes: bytes is NULL");
+    int const rc = check_gemm_shape("fso_gemm_mxfp8_ws_bytes", m, n, k);
+    if (rc != 0) return rc;
+    *bytes = m == 0 ? 0 : plan_dense(m, n, k, sm_count()).ws_bytes;
+    return 0;
+}
+
+int fso_gemm_mxfp8(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
+    int64_t k, void* ws, int64_t ws_bytes, void* stream)
+{
+    int const rc = check_gemm_shape("fso_gemm_mxfp8", m, n, k);
+    if (rc != 0) return rc;
+    if (m == 0) return 0;
+    FSO_REQUIRE(a && sfa && w && sfw && d, "fso_gemm_mxfp8: NULL pointer");
+    FSO_REQUIRE(aligned16(a) && aligned16(sfa) && aligned16(w) && aligned16(sfw) && aligned16(d),
+        "fso_gemm_mxfp8: every operand must be 16-byte aligned (TMA reads them in place)");
+    FSO_REQUIRE(ws == nullptr || aligned16(ws), "fso_gemm_mxfp8: the workspace must be 16-byte aligned");
+    return launch_dense(a, sfa, w, sfw, d, m, n, k, ws, ws_bytes, as_stream(stream));
+}
+
+int fso_moe_plan_make(int64_t tokens, int64_t topk, int64_t num_experts, fso_moe_plan* plan)
+{
+    FSO_REQUIRE(plan != nullptr, "fso_moe_plan_make: plan is NULL");
+    FSO_REQUIRE(tokens >= 0 && topk >= 1 && num_experts >= 1 && num_experts <= 1024,
+        "fso_moe_plan_make: tokens >= 0, topk >= 1, 1 <= num_experts <= 1024 required");
+    int64_t const pairs = tokens * topk;
+    FSO_REQUIRE(pairs < (1ll << 24), "fso_moe_plan_make: tokens * topk = %lld is beyond the routing kernels' range",
+        static_cast<long long>(pairs));
+    int64_t const active = num_experts < pairs ? num_experts : pairs;
+    int64_t nb = (pairs + 127 * active) / 128;
+    if (nb < 1) nb = 1;
+    plan->pairs = pairs;
+    plan->num_blocks = nb;
+    plan->rows = 128 * (nb + 1);
+    plan->route_scratch_bytes = pairs > kRouteSeg ? ((pairs + kRouteSeg - 1) / kRouteSeg) * num_experts * 4 : 0;
+    return 0;
+}
+
+int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_experts, int64_t num_blocks,
+    int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* scratch,
+    int64_t scratch_bytes, void* stream)
+{
+    fso_moe_plan pl;
+    int const rc = fso_moe_plan_make(tokens, topk, num_experts, &pl);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(num_blocks >= pl.num_blocks, "fso_moe_route: num_blocks = %lld is below the bound %lld of this call",
+        static_cast<long long>(num_blocks), static_cast<long long>(pl.num_blocks));
+    FSO_REQUIRE(masked_m && blk0 && blk_expert && (pl.pairs == 0 || (ids && slot_of_flat)), "fso_moe_route: NULL pointer");
+    cudaStream_t const st = as_stream(stream);
+    int const e = static_cast<int>(num_experts), nb = static_cast<int>(num_blocks), pairs = static_cast<int>(pl.pairs);
+    size_t const smem = static_cast<size_t>(64) * e;   // [32][E] uint16
+    if (pairs <= kRouteSeg) {
+        route_small_kernel<<<1, kRouteSeg, smem, st>>>(ids, pairs, e, nb, masked_m, blk0, slot_of_flat, blk_expert);
+        return launch_status("route_small_kernel");
+    }
+    FSO_REQUIRE(scratch != nullptr && scratch_bytes >= pl.route_scratch_bytes && (reinterpret_cast<uintptr_t>(scratch) & 3u) == 0,
+        "fso_moe_route: this call needs %lld bytes of 4-byte aligned scratch", static_cast<long long>(pl.route_scratch_bytes));
+    int const segs = (pairs + kRouteSeg - 1) / kRouteSeg;
+    int32_t* seg = static_cast<int32_t*>(scratch);
+    static std::atomic<uint64_t> done_count{0}, done_place{0};
+    if (smem > 48 * 1024) {
+        int r2 = ensure_smem_attr(route_count_kernel, static_cast<int>(smem), done_count);
+        if (r2 != 0) return r2;
+        r2 = ensure_smem_attr(route_place_kernel, static_cast<int>(smem), done_place);
+        if (r2 != 0) return r2;
+    }
+    route_count_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg);
+    route_scan_kernel<<<1, kRouteSeg, 0, st>>>(seg, segs, e, nb, masked_m, blk0, blk_expert);
+    route_place_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg, blk0, slot_of_flat);
+    return launch_status("route kernels");
+}
+
+int fso_moe_gather_quant(const void* hidden, const int32_t* slot_of_flat, int64_t tokens, int64_t topk, int64_t h,
+    int64_t rows, void* hq, void* sh, void* stream)
+{
+    FSO_REQUIRE(tokens >= 0 && topk >= 1 && h > 0 && h % 128 == 0 && rows > 0 && rows % 128 == 0,
+        "fso_moe_gather_quant: H a multiple of 128 and rows a multiple of 128 required");
+    if (tokens == 0) return 0;
+    FSO_REQUIRE(hidden && slot_of_flat && hq && sh, "fso_moe_gather_quant: NULL pointer");
+    FSO_REQUIRE(aligned16(hidden) && aligned16(hq) && (reinterpret_cast<uintptr_t>(sh) & 3u) == 0,
+        "fso_moe_gather_quant: hidden and hq must be 16-byte aligned");
+    constexpr int kUnroll = 2;
+    int const kb = static_cast<int>(h / 128);
+    int64_t const halves = (tokens * kb + kUnroll - 1) / kUnroll;
+    int64_t const blocks = (halves * 16 + 255) / 256;
+    gather_quant_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
+        static_cast<const uint4*>(hidden), slot_of_flat, tokens, static_cast<int>(topk), kb, static_cast<uint2*>(hq),
+        static_cast<uint32_t*>(sh));
+    return launch_status("gather_quant_kernel");
+}
+
+static int check_grouped(const char* op, int64_t num_experts, int64_t h, int64_t inter, int64_t num_blocks, int64_t rows)
+{
+    FSO_REQUIRE(num_experts >= 1 && num_experts <= 1024 && h > 0 && inter > 0 && h % 128 == 0 && inter % 128 == 0,
+        "%s: 1 <= E <= 1024 and H, I multiples of 128 required", op);
+    FSO_REQUIRE(num_blocks >= 1 && rows >= 128 * num_blocks && rows % 128 == 0,
+        "%s: rows = %lld must be a multiple of 128 covering num_blocks = %lld blocks", op, static_cast<long long>(rows),
+        static_cast<long long>(num_blocks));
+    FSO_REQUIRE(num_experts * 2 * inter < (1ll << 31) && rows < (1ll << 31), "%s: dimension too large", op);
+    return 0;
+}
+
+int fso_moe_fc1_swiglu(const void* hq, const void* sh, const void* w13, const void* sw13, const int32_t* blk0,
+    const int32_t* blk_expert, int64_t num_experts, int64_t h, int64_t inter, int64_t num_blocks, int64_t rows,
+    void* dq, void* sd, void* stream)
+{
+    int const rc = check_grouped("fso_moe_fc1_swiglu", num_experts, h, inter, num_blocks, rows);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(hq && sh && w13 && sw13 && blk0 && blk_expert && dq && sd, "fso_moe_fc1_swiglu: NULL pointer");
+    FSO_REQUIRE(aligned16(hq) && aligned16(sh) && aligned16(w13) && aligned16(sw13) && aligned16(dq) && aligned16(sd),
+        "fso_moe_fc1_swiglu: every operand must be 16-byte aligned");
+    return launch_grouped(hq, sh, w13, sw13, blk0, blk_expert, num_experts, 2 * inter, h, num_blocks, rows, dq, sd, true,
+        as_stream(stream));
+}
+
+int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2, const int32_t* blk0,
+    const int32_t* blk_expert, int64_t num_experts, int64_t h, int64_t inter, int64_t num_blocks, int64_t rows,
+    void* dn, void* stream)
+{
+    int const rc = check_grouped("fso_moe_fc2", num_experts, h, inter, num_blocks, rows);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(dq && sd && w2 && sw2 && blk0 && blk_expert && dn, "fso_moe_fc2: NULL pointer");
+    FSO_REQUIRE(aligned16(dq) && aligned16(sd) && aligned16(w2) && aligned16(sw2) && aligned16(dn),
+        "fso_moe_fc2: every operand must be 16-byte aligned");
+    return launch_grouped(dq, sd, w2, sw2, blk0, blk_expert, num_experts, h, inter, num_blocks, rows, dn, nullptr, false,
+        as_stream(stream));
+}
+
+int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,
+    const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, void* stream)
+{
+    FSO_REQUIRE(tokens >= 0 && topk >= 1 && h > 0 && h % 8 == 0, "fso_moe_combine: H must be a multiple of 8");
+    if (tokens == 0) return 0;
+    FSO_REQUIRE(dn && slot_of_flat && topk_w && out, "fso_moe_combine: NULL pointer");
+    FSO_REQUIRE(aligned16(dn) && aligned16(out) && (bias == nullptr || aligned16(bias)),
+        "fso_moe_combine: dn, out and bias must be 16-byte aligned");
+    FSO_REQUIRE(bias != nullptr || bias_scale == nullptr, "fso_moe_combine: bias_scale scales bias and needs it");
+    int const h8 = static_cast<int>(h / 8);
+    int64_t const total = tokens * h8;
+    combine_kernel<8><<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+        static_cast<const uint4*>(dn), slot_of_flat, topk_w, static_cast<const uint4*>(bias), bias_scale,
+        static_cast<uint4*>(out), tokens, static_cast<int>(topk), h8);
+    return launch_status("combine_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,254 @@
+// MoE glue kernels around the grouped GEMMs: compact routing (deterministic order), token gather + quantize,
+// and the top-k weighted un-permute / reduce. All of them are integer / byte work bound by HBM or latency.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "quant.cuh"
+
+namespace fso {
+
+constexpr int kRouteSeg = 1024;   // pairs per routing segment == threads per routing CTA
+
+// Rank of every pair of one 1024-pair segment among the segment's pairs of the same expert, in ascending flat
+// index, and the segment's per-expert totals.
+//   in : e (expert of this thread's pair, any value when !valid)
+//   out: returns the rank; s_cnt[x] = pairs of expert x in this segment (valid after the function returns)
+// s_wbase is [32][num_experts] uint16 scratch. Deterministic: no atomics.
+__device__ __forceinline__ int segment_rank(int e, bool valid, int num_experts, int* s_cnt, uint16_t* s_wbase)
+{
+    int const tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < 32 * num_experts; i += kRouteSeg) s_wbase[i] = 0;
+    __syncthreads();
+    unsigned const peers = __match_any_sync(0xFFFFFFFFu, valid ? e : -1);
+    int const rank_w = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank_w == 0) s_wbase[warp * num_experts + e] = static_cast<uint16_t>(__popc(peers));
+    __syncthreads();
+    for (int x = tid; x < num_experts; x += kRouteSeg) {
+        int run = 0;
+#pragma unroll 4
+        for (int w = 0; w < 32; ++w) {
+            int const c = s_wbase[w * num_experts + x];
+            s_wbase[w * num_experts + x] = static_cast<uint16_t>(run);
+            run += c;
+        }
+        s_cnt[x] = run;
+    }
+    __syncthreads();
+    return valid ? static_cast<int>(s_wbase[warp * num_experts + e]) + rank_w : 0;
+}
+
+// Exclusive scan over experts of ceil(cnt / 128) by one 1024-thread CTA (num_experts <= 1024); thread x returns
+// the prefix of expert x, *total gets the sum. s_tmp is 33 ints.
+__device__ __forceinline__ int block_prefix_blocks(int cnt, int* s_tmp, int* total)
+{
+    int const tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int const v = (cnt + 127) >> 7;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int const o = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+        if (lane >= d) inc += o;
+    }
+    if (lane == 31) s_tmp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = s_tmp[lane];
+        int winc = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int const o = __shfl_up_sync(0xFFFFFFFFu, winc, d);
+            if (lane >= d) winc += o;
+        }
+        s_tmp[lane] = winc - w;
+        if (lane == 31) s_tmp[32] = winc;
+    }
+    __syncthreads();
+    *total = s_tmp[32];
+    return s_tmp[warp] + inc - v;
+}
+
+__device__ __forceinline__ void fill_block_experts(int x, int num_experts, int start, int cnt, int total_blocks,
+    int num_blocks, int32_t* blk_expert)
+{
+    if (x < num_experts) {
+        int const nb = (cnt + 127) >> 7;
+        for (int b = start; b < start + nb && b < num_blocks; ++b) blk_expert[b] = x;
+    }
+    for (int b = total_blocks + x; b < num_blocks; b += kRouteSeg) blk_expert[b] = -1;
+}
+
+// pairs <= 1024: everything in one CTA.
+__global__ void __launch_bounds__(kRouteSeg) route_small_kernel(const int32_t* __restrict__ ids, int pairs,
+    int num_experts, int num_blocks, int32_t* __restrict__ masked_m, int32_t* __restrict__ blk0,
+    int32_t* __restrict__ slot_of_flat, int32_t* __restrict__ blk_expert)
+{
+    extern __shared__ uint16_t s_wbase[];
+    __shared__ int s_cnt[1024];
+    __shared__ int s_blk[1024];
+    __shared__ int s_tmp[33];
+    int const tid = threadIdx.x;
+    int const e = tid < pairs ? ids[tid] : -1;
+    bool const valid = e >= 0 && e < num_experts;
+    int const rank = segment_rank(e, valid, num_experts, s_cnt, s_wbase);
+    int const cnt = tid < num_experts ? s_cnt[tid] : 0;
+    int total;
+    int const start = block_prefix_blocks(cnt, s_tmp, &total);
+    if (tid < num_experts) {
+        masked_m[tid] = cnt;
+        blk0[tid] = start;
+        s_blk[tid] = start;
+    }
+    if (tid == 0) blk0[num_experts] = total;
+    fill_block_experts(tid, num_experts, start, cnt, total, num_blocks, blk_expert);
+    __syncthreads();
+    if (tid < pairs) slot_of_flat[tid] = valid ? s_blk[e] * 128 + rank : -1;
+}
+
+// pairs > 1024, pass 1: per-segment per-expert counts -> seg_cnt[segment][expert].
+__global__ void __launch_bounds__(kRouteSeg) route_count_kernel(const int32_t* __restrict__ ids, int pairs,
+    int num_experts, int32_t* __restrict__ seg_cnt)
+{
+    extern __shared__ uint16_t s_wbase[];
+    __shared__ int s_cnt[1024];
+    int const i = blockIdx.x * kRouteSeg + threadIdx.x;
+    int const e = i < pairs ? ids[i] : -1;
+    bool const valid = e >= 0 && e < num_experts;
+    (void)segment_rank(e, valid, num_experts, s_cnt, s_wbase);
+    for (int x = threadIdx.x; x < num_experts; x += kRouteSeg) seg_cnt[blockIdx.x * num_experts + x] = s_cnt[x];
+}
+
+// pass 2 (one CTA): seg_cnt -> exclusive prefix over segments (in place), expert totals, block prefix, block table.
+__global__ void __launch_bounds__(kRouteSeg) route_scan_kernel(int32_t* __restrict__ seg_cnt, int segments,
+    int num_experts, int num_blocks, int32_t* __restrict__ masked_m, int32_t* __restrict__ blk0,
+    int32_t* __restrict__ blk_expert)
+{
+    __shared__ int s_tmp[33];
+    int const tid = threadIdx.x;
+    int cnt = 0;
+    if (tid < num_experts) {
+        for (int s = 0; s < segments; ++s) {
+            int const c = seg_cnt[s * num_experts + tid];
+            seg_cnt[s * num_experts + tid] = cnt;
+            cnt += c;
+        }
+    }
+    int total;
+    int const start = block_prefix_blocks(cnt, s_tmp, &total);
+    if (tid < num_experts) {
+        masked_m[tid] = cnt;
+        blk0[tid] = start;
+    }
+    if (tid == 0) blk0[num_experts] = total;
+    fill_block_experts(tid, num_experts, start, cnt, total, num_blocks, blk_expert);
+}
+
+// pass 3: place every pair.
+__global__ void __launch_bounds__(kRouteSeg) route_place_kernel(const int32_t* __restrict__ ids, int pairs,
+    int num_experts, const int32_t* __restrict__ seg_base, const int32_t* __restrict__ blk0,
+    int32_t* __restrict__ slot_of_flat)
+{
+    extern __shared__ uint16_t s_wbase[];
+    __shared__ int s_cnt[1024];
+    int const i = blockIdx.x * kRouteSeg + threadIdx.x;
+    int const e = i < pairs ? ids[i] : -1;
+    bool const valid = e >= 0 && e < num_experts;
+    int const rank = segment_rank(e, valid, num_experts, s_cnt, s_wbase);
+    if (i < pairs)
+        slot_of_flat[i] = valid ? blk0[e] * 128 + seg_base[blockIdx.x * num_experts + e] + rank : -1;
+}
+
+// ---------------------------------------------------------------------------------------------------- gather + quantize
+
+// One (token, 128-element chunk) per half-warp and step: the token is quantized once and its codes and scale word
+// are stored to each of its top-k compact rows (skipped pairs store nothing).
+template <int kUnroll>
+__global__ void __launch_bounds__(256) gather_quant_kernel(const uint4* __restrict__ hidden,
+    const int32_t* __restrict__ slot_of_flat, int64_t tokens, int topk, int kb, uint2* __restrict__ hq,
+    uint32_t* __restrict__ sh)
+{
+    int const sub = threadIdx.x & 15;
+    int64_t const half = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+    int64_t const total = tokens * kb;
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        int64_t const c = half * kUnroll + u;
+        v[u] = c < total ? __ldg(hidden + c * 16 + sub) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        int64_t const c = half * kUnroll + u;
+        uint2 codes;
+        uint32_t const byte = quant8_shared4(v[u], codes);
+        uint32_t const word = word_from_16lanes(byte, sub);
+        if (c < total) {
+            int64_t const t = c / kb;
+            int const kp = static_cast<int>(c - t * kb);
+            for (int j = 0; j < topk; ++j) {
+                int const slot = __ldg(slot_of_flat + t * topk + j);
+                if (slot >= 0) {
+                    hq[(static_cast<int64_t>(slot) * kb + kp) * 16 + sub] = codes;
+                    if (sub == 0) sh[sf_word_index(slot, kp, kb)] = word;
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- combine
+
+// One (token, 8 columns) per thread: fp32 FMA chain over the token's top-k rows in ascending j, then the bias term,
+// one rounding to bf16.
+template <int kMaxTopk>
+__global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ dn,
+    const int32_t* __restrict__ slot_of_flat, const float* __restrict__ topk_w, const uint4* __restrict__ bias,
+    const float* __restrict__ bias_scale, uint4* __restrict__ out, int64_t tokens, int topk, int h8)
+{
+    int64_t const idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= tokens * h8) return;
+    int64_t const t = idx / h8;
+    int const c = static_cast<int>(idx - t * h8);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto fma_row = [&](uint4 const& raw, float w) {
+        uint32_t const ws[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = fmaf(w, __uint_as_float(ws[i] << 16), acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, __uint_as_float(ws[i] & 0xFFFF0000u), acc[2 * i + 1]);
+        }
+    };
+    if (topk <= kMaxTopk) {
+        int slots[kMaxTopk];
+        float ws[kMaxTopk];
+        uint4 raws[kMaxTopk];
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (j < topk) {
+                slots[j] = __ldg(slot_of_flat + t * topk + j);
+                ws[j] = __ldg(topk_w + t * topk + j);
+            }
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (j < topk) raws[j] = slots[j] >= 0 ? __ldg(dn + static_cast<int64_t>(slots[j]) * h8 + c)
+                                                   : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (j < topk && slots[j] >= 0) fma_row(raws[j], ws[j]);
+    } else {
+        for (int j = 0; j < topk; ++j) {
+            int const slot = __ldg(slot_of_flat + t * topk + j);
+            if (slot >= 0) fma_row(__ldg(dn + static_cast<int64_t>(slot) * h8 + c), __ldg(topk_w + t * topk + j));
+        }
+    }
+    if (bias != nullptr) fma_row(__ldg(bias + t * h8 + c), bias_scale != nullptr ? __ldg(bias_scale + t) : 1.f);
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    out[idx] = o;
+}
+
+}  // namespace fso

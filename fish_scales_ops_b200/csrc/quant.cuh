@@ -1,0 +1,251 @@
+// HBM-bound quantizers: bf16 -> MXFP8 (1x32 blocks, UE8M0 scales), block-FP8 128x128 -> MXFP8, and the
+// checkpoint scale packer. All of them write the scale words straight into the atom layout the GEMM's
+// scale-factor copy reads (one contiguous 512-byte block per 128 rows x 128 K).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace fso {
+
+// ---------------------------------------------------------------------------------------------------- the rule
+
+// Scale byte and quant scale of a block from its amax (already floored at 1e-10f). Division-free form of
+// b = exp(1 / (448 / amax)) + (mantissa != 0): with E, f the exponent and mantissa fields of amax,
+// b = E - (f <= 0x600000 ? 8 : 7), clamped to [0, 254]; quant scale 2^(127 - b). Equal to the two-division form
+// for every fp32 amax >= 1e-10f (checked exhaustively on the host).
+__device__ __forceinline__ uint32_t e8m0_from_amax(float amax, float& quant_scale)
+{
+    uint32_t const bits = __float_as_uint(amax);
+    int const e = static_cast<int>((bits >> 23) & 0xFFu);
+    uint32_t const f = bits & 0x7FFFFFu;
+    int byte = e - (f <= 0x600000u ? 8 : 7);
+    byte = max(0, min(254, byte));
+    uint32_t qbits = static_cast<uint32_t>(254 - byte) << 23;
+    if (byte == 254) qbits = 0x00400000u;    // 2^-127, a subnormal
+    if (byte == 0) qbits = 0x3F800000u;
+    quant_scale = __uint_as_float(qbits);
+    return static_cast<uint32_t>(byte);
+}
+
+__device__ __forceinline__ uint32_t fp8x4(float v0, float v1, float v2, float v3)
+{
+    uint32_t const lo = __nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E4M3);
+    uint32_t const hi = __nv_cvt_float2_to_fp8x2(make_float2(v2, v3), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    __nv_bfloat162 const v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ int64_t sf_word_index(int64_t m, int64_t kp, int64_t kb)
+{
+    int64_t const r = m & 127;
+    return ((m >> 7) * kb + kp) * 128 + (r & 31) * 4 + (r >> 5);
+}
+
+// max |.| of the two bf16 halves of each word, as 15-bit patterns (monotonic in magnitude for non-NaN values)
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b)
+{
+    return __vmaxu2(a & 0x7FFF7FFFu, b & 0x7FFF7FFFu);
+}
+
+// Quantizes the 8 bf16 values of `v` (one 16-byte load) of a 32-element block shared by 4 adjacent lanes.
+// Returns the 8 codes in `out` and the block's byte (same value on the 4 lanes).
+__device__ __forceinline__ uint32_t quant8_shared4(uint4 const& v, uint2& out)
+{
+    uint32_t m = absmax_bf16x2(absmax_bf16x2(v.x, v.y), absmax_bf16x2(v.z, v.w));
+    m = max(m & 0xFFFFu, m >> 16);
+    m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    float const amax = fmaxf(__uint_as_float(m << 16), 1e-10f);
+    float qs;
+    uint32_t const byte = e8m0_from_amax(amax, qs);
+    auto lo = [](uint32_t w) { return __uint_as_float(w << 16); };
+    auto hi = [](uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); };
+    out.x = fp8x4(__fmul_rn(lo(v.x), qs), __fmul_rn(hi(v.x), qs), __fmul_rn(lo(v.y), qs), __fmul_rn(hi(v.y), qs));
+    out.y = fp8x4(__fmul_rn(lo(v.z), qs), __fmul_rn(hi(v.z), qs), __fmul_rn(lo(v.w), qs), __fmul_rn(hi(v.w), qs));
+    return byte;
+}
+
+// The scale word of a 128-element chunk handled by 16 adjacent lanes (4 lanes per block): every lane passes its
+// block's byte, every lane gets the word.
+__device__ __forceinline__ uint32_t word_from_16lanes(uint32_t byte, int sub16)
+{
+    uint32_t w = byte << (8 * (sub16 >> 2));
+    w |= __shfl_xor_sync(0xFFFFFFFFu, w, 4);
+    w |= __shfl_xor_sync(0xFFFFFFFFu, w, 8);
+    return w;
+}
+
+// ---------------------------------------------------------------------------------------------------- bf16 -> MXFP8
+
+// One 128-element chunk (row, kp) per half-warp and step; every half-warp owns kUnroll consecutive chunks so that
+// kUnroll independent 16-byte loads per thread are in flight. Rows in [m, m_pad) only get their zero words.
+template <int kUnroll>
+__global__ void __launch_bounds__(256) quantize_1x32_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
+    uint32_t* __restrict__ sf, int64_t m, int64_t m_pad, int kb, int64_t interleave_i)
+{
+    int const sub = threadIdx.x & 15;
+    int64_t const half = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+    int64_t const total = m_pad * kb;
+    int64_t const c0 = half * kUnroll;
+
+    uint4 v[kUnroll];
+    int64_t row[kUnroll];
+    int kp[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        int64_t const c = c0 + u;
+        row[u] = c / kb;
+        kp[u] = static_cast<int>(c - row[u] * kb);
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (c < total && row[u] < m) {
+            int64_t src = row[u];
+            if (interleave_i > 0) {
+                int64_t const two_i = 2 * interleave_i;
+                int64_t const g = src / two_i, o = src - g * two_i;
+                src = g * two_i + ((o & 1) ? interleave_i + (o >> 1) : (o >> 1));
+            }
+            v[u] = __ldg(x + (src * kb + kp[u]) * 16 + sub);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        int64_t const c = c0 + u;
+        uint2 codes;
+        uint32_t const byte = quant8_shared4(v[u], codes);
+        uint32_t const word = word_from_16lanes(byte, sub);
+        if (c < total) {
+            bool const live = row[u] < m;
+            if (live) q[(row[u] * kb + kp[u]) * 16 + sub] = codes;
+            if (sub == 0) sf[sf_word_index(row[u], kp[u], kb)] = live ? word : 0u;
+        }
+    }
+}
+
+inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int64_t k, int64_t interleave_i,
+    cudaStream_t stream)
+{
+    constexpr int kUnroll = 4;
+    int64_t const m_pad = (m + 127) / 128 * 128;
+    int const kb = static_cast<int>(k / 128);
+    int64_t const halves = (m_pad * kb + kUnroll - 1) / kUnroll;
+    int64_t const blocks = (halves * 16 + 255) / 256;
+    quantize_1x32_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const uint4*>(x), static_cast<uint2*>(q), static_cast<uint32_t*>(sf), m, m_pad, kb, interleave_i);
+    return launch_status("fso_quantize_1x32");
+}
+
+// ---------------------------------------------------------------------------------------------------- block-FP8 -> MXFP8
+
+// 16 e4m3 codes per thread (one 16-byte load); 2 lanes per 32-element block, 8 lanes per 128-element chunk.
+// value = bf16_rne(float(code) * s_tile) in fp32 with one rounding, then the 1x32 rule on those bf16 values.
+__global__ void __launch_bounds__(256) requant_bs128_kernel(const uint4* __restrict__ wq, const float* __restrict__ s128,
+    uint4* __restrict__ q, uint32_t* __restrict__ sf, int64_t n, int kb, int64_t interleave_i)
+{
+    int const sub = threadIdx.x & 7;
+    int64_t const c = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;   // chunk (row, kp)
+    int64_t const total = n * kb;
+    bool const live = c < total;
+    int64_t const row = live ? c / kb : 0;
+    int const kp = live ? static_cast<int>(c - row * kb) : 0;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    float s = 0.f;
+    if (live) {
+        int64_t src = row;
+        if (interleave_i > 0) {
+            int64_t const two_i = 2 * interleave_i;
+            int64_t const g = src / two_i, o = src - g * two_i;
+            src = g * two_i + ((o & 1) ? interleave_i + (o >> 1) : (o >> 1));
+        }
+        v = __ldg(wq + (src * kb + kp) * 8 + sub);
+        s = __ldg(s128 + (src >> 7) * kb + kp);
+    }
+    float f[16];
+    uint32_t const w[4] = {v.x, v.y, v.z, v.w};
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            __half2_raw const hr = __nv_cvt_fp8x2_to_halfraw2(
+                static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
+            float2 const p = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+            float const a = __bfloat162float(__float2bfloat16_rn(__fmul_rn(p.x, s)));
+            float const b = __bfloat162float(__float2bfloat16_rn(__fmul_rn(p.y, s)));
+            f[i * 4 + h * 2] = a;
+            f[i * 4 + h * 2 + 1] = b;
+            amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+        }
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, 1e-10f);
+    float qs;
+    uint32_t const byte = e8m0_from_amax(amax, qs);
+    uint4 out;
+    out.x = fp8x4(__fmul_rn(f[0], qs), __fmul_rn(f[1], qs), __fmul_rn(f[2], qs), __fmul_rn(f[3], qs));
+    out.y = fp8x4(__fmul_rn(f[4], qs), __fmul_rn(f[5], qs), __fmul_rn(f[6], qs), __fmul_rn(f[7], qs));
+    out.z = fp8x4(__fmul_rn(f[8], qs), __fmul_rn(f[9], qs), __fmul_rn(f[10], qs), __fmul_rn(f[11], qs));
+    out.w = fp8x4(__fmul_rn(f[12], qs), __fmul_rn(f[13], qs), __fmul_rn(f[14], qs), __fmul_rn(f[15], qs));
+    uint32_t word = byte << (8 * (sub >> 1));
+    word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
+    word |= __shfl_xor_sync(0xFFFFFFFFu, word, 4);
+    if (live) {
+        q[(row * kb + kp) * 8 + sub] = out;
+        if (sub == 0) sf[sf_word_index(row, kp, kb)] = word;
+    }
+}
+
+inline int launch_requant_bs128(const void* wq, const float* s128, void* q, void* sf, int64_t n, int64_t k,
+    int64_t interleave_i, cudaStream_t stream)
+{
+    int const kb = static_cast<int>(k / 128);
+    int64_t const blocks = (n * kb * 8 + 255) / 256;
+    requant_bs128_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(wq), s128,
+        static_cast<uint4*>(q), static_cast<uint32_t*>(sf), n, kb, interleave_i);
+    return launch_status("fso_requant_bs128_to_mx");
+}
+
+// ---------------------------------------------------------------------------------------------------- scale packer
+
+// One thread per output word (group, padded row, kp); padded rows get zero words.
+__global__ void __launch_bounds__(256) pack_ue8m0_kernel(const uint8_t* __restrict__ s, uint32_t* __restrict__ out,
+    int64_t g, int64_t n, int64_t n_pad, int kb, int64_t interleave_i)
+{
+    int64_t const idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    int64_t const slab = n_pad * kb;
+    if (idx >= g * slab) return;
+    int64_t const e = idx / slab;
+    int64_t const rem = idx - e * slab;
+    int64_t const r = rem / kb;
+    int const kp = static_cast<int>(rem - r * kb);
+    uint32_t word = 0;
+    if (r < n) {
+        int64_t src = r;
+        if (interleave_i > 0) src = (r & 1) ? interleave_i + (r >> 1) : (r >> 1);
+        const uint8_t* b = s + ((e * n + src) * kb + kp) * 4;
+        word = static_cast<uint32_t>(b[0]) | (static_cast<uint32_t>(b[1]) << 8) | (static_cast<uint32_t>(b[2]) << 16)
+            | (static_cast<uint32_t>(b[3]) << 24);
+    }
+    out[e * slab + sf_word_index(r, kp, kb)] = word;
+}
+
+inline int launch_pack_ue8m0(const void* s, void* out, int64_t g, int64_t n, int64_t k, int64_t interleave_i,
+    cudaStream_t stream)
+{
+    int const kb = static_cast<int>(k / 128);
+    int64_t const n_pad = (n + 127) / 128 * 128;
+    int64_t const total = g * n_pad * kb;
+    pack_ue8m0_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(s), static_cast<uint32_t*>(out), g, n, n_pad, kb, interleave_i);
+    return launch_status("fso_pack_ue8m0");
+}
+
+}  // namespace fso

@@ -1,0 +1,115 @@
+/*
+ * fso_b200: the C ABI of the B200 (sm_100a) MXFP8 dense / MoE path.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream (cudaStream_t passed as void*), launches on
+ * that stream and returns without synchronizing. Nothing here allocates device memory: outputs, workspaces and
+ * scratch are the caller's. Return value: 0 on success, a positive cudaError_t when a CUDA call failed, a
+ * negative FSO_ERR_* code otherwise; fso_b200_last_error() gives the text of the last failure on the calling
+ * host thread. A refused call (FSO_ERR_INVALID) has launched nothing.
+ *
+ * Layouts (identical to the reference's sm_100 forms, python/fish_scales_ops/include/fso/activation_contract.h):
+ *   quantized tensor  e4m3 bytes [rows, K], row-major, 16-byte aligned, K % 128 == 0
+ *   scale words       int32, align(rows,128) * K/128 of them; word(m, kp) packs the UE8M0 bytes of the 32-element
+ *                     blocks 4kp..4kp+3 of row m (lowest block in the lowest byte) and sits at
+ *                     ((m/128) * (K/128) + kp) * 128 + (m%32) * 4 + (m%128)/32; the padded rows' words are zero.
+ *
+ * Each declaration names the reference interface it replaces (path inside the reference project : line).
+ */
+#ifndef FSO_B200_H
+#define FSO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FSO_ERR_INVALID (-1)       /* malformed argument; nothing was launched */
+#define FSO_ERR_UNSUPPORTED (-2)   /* this device or shape is not served */
+#define FSO_ERR_INTERNAL (-3)
+
+int fso_b200_version(void);
+const char* fso_b200_last_error(void);
+
+/* Reads (and clears) the device-side status word of the current device: 0, or the code of a bounded wait that ran
+ * out inside a kernel. Synchronizes the device; meant for tests and health checks, never for the hot path. */
+int fso_b200_device_status(int* status);
+
+/* bf16 [M, K] -> e4m3 [M, K] + scale words (1x32 MXFP8 rule, bit-exact with the reference).
+ * interleave_i > 0: x is G stacked [2*I, K] expert matrices in [gate; up] row order and output rows 2j / 2j+1 of
+ * each expert take its rows j / I+j (the fused-FC1 weight order).
+ * Replaces: op quantize_1x32_packed, csrc/gemm/ops/mxfp8.cu:279-321 -> fp8bs_quantize_1x32_packed,
+ * csrc/gemm/ops/quant_kernels.cu:776-820; expert form python/fish_scales_ops/gemm/mxfp8.py:1511-1582. */
+int fso_quantize_1x32(const void* x_bf16, void* xq, void* sf, int64_t m, int64_t k, int64_t interleave_i,
+                      void* stream);
+
+/* Block-FP8 checkpoint (e4m3 [N, K] + one fp32 scale per 128x128 tile, [N/128, K/128]) -> MXFP8: each value is
+ * bf16_rne(float(fp8) * scale) and then goes through the 1x32 rule. N % 128 == 0. interleave_i as in
+ * fso_quantize_1x32 (stacked experts, I % 128 == 0; the tile scale follows the source row).
+ * Replaces: _dequantize_block_fp8 + _requantize_block_fp8, python/fish_scales_ops/dense/__init__.py:422-462,
+ * and python/fish_scales_ops/moe/__init__.py:400-407 for experts. */
+int fso_requant_bs128_to_mx(const void* wq, const float* s128, void* out_q, void* out_sf, int64_t n, int64_t k,
+                            int64_t interleave_i, void* stream);
+
+/* Checkpoint UE8M0 bytes uint8 [G, N, K/32] -> scale words, one atom slab of align(N,128)*K/128 words per group;
+ * interleave_i as in fso_quantize_1x32 (applied to the rows of every group).
+ * Replaces: _ue8m0_scale_handle, python/fish_scales_ops/gemm/mxfp8.py:718-768. */
+int fso_pack_ue8m0(const void* sf_u8, void* out_sf, int64_t g, int64_t n, int64_t k, int64_t interleave_i,
+                   void* stream);
+
+/* Dense GEMM D[M, N] (bf16) = A[M, K] * W[N, K]^T over MXFP8 operands with fp32 accumulation.
+ * fso_gemm_mxfp8_ws_bytes gives the workspace the split-K route of this shape needs (0 when it takes none);
+ * ws may be NULL when that is 0. N % 128 == 0, K % 128 == 0.
+ * Replaces: linear_mxfp8_raw, csrc/gemm/ops/mxfp8.cu:432-541 -> launch_sm100_mxfp8_dispatch (mxfp8.cu:48-51) ->
+ * gemm_dispatch_sm100_mxfp8, csrc/gemm/include/blockscale_gemm/arch/sm100/mxfp8/dispatch.cuh:1430-1443. */
+int fso_gemm_mxfp8_ws_bytes(int64_t m, int64_t n, int64_t k, int64_t* bytes);
+int fso_gemm_mxfp8(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
+                   int64_t k, void* ws, int64_t ws_bytes, void* stream);
+
+/* Host-static sizes of one MoE layer call (functions of the argument shapes only).
+ * Replaces: _mxfp8_layer_plan / moe_compact_num_blocks, python/fish_scales_ops/gemm/mxfp8.py:1653-1728, 1228-1239. */
+typedef struct fso_moe_plan {
+    int64_t pairs;          /* tokens * topk */
+    int64_t num_blocks;     /* bound on the 128-row blocks in use */
+    int64_t rows;           /* rows of every compact intermediate: 128 * (num_blocks + 1) */
+    int64_t route_scratch_bytes;   /* scratch fso_moe_route needs (0 for small calls) */
+} fso_moe_plan;
+int fso_moe_plan_make(int64_t tokens, int64_t topk, int64_t num_experts, fso_moe_plan* plan);
+
+/* Compact routing. ids int32 [tokens * topk]; ids outside [0, E) are skipped (slot -1).
+ * masked_m[E] rows per expert; blk0[E+1] exclusive prefix of ceil(rows/128), blk0[E] = blocks in use;
+ * slot_of_flat[tokens*topk] = blk0[e]*128 + rank, rank = position among the expert's pairs in ascending flat
+ * index (deterministic); blk_expert[num_blocks] expert of each block, -1 past the blocks in use.
+ * Replaces: moe_build_routing_compact, csrc/gemm/ops/moe_glue.cu:2651-2823. */
+int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_experts, int64_t num_blocks,
+                  int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* scratch,
+                  int64_t scratch_bytes, void* stream);
+
+/* Row gather + 1x32 quantize into the compact buffers: row slot_of_flat[i] of hq / sh takes token i / topk.
+ * hq e4m3 [rows, H], sh scale words of a [rows, H] tensor. Rows no pair maps to are not written.
+ * Replaces: quantize_1x32_grouped_gather_out, csrc/gemm/ops/mxfp8_compact.cu:206. */
+int fso_moe_gather_quant(const void* hidden_bf16, const int32_t* slot_of_flat, int64_t tokens, int64_t topk,
+                         int64_t h, int64_t rows, void* hq, void* sh, void* stream);
+
+/* Grouped FC1 with the fused SiLU(gate)*up requantize: for every block b in use, rows [128b, 128b+128) of hq times
+ * w13[blk_expert[b]]^T (rows interleaved gate/up) -> dq e4m3 [rows, I] + sd scale words of a [rows, I] tensor.
+ * Replaces: linear_mxfp8_grouped_compact_swiglu, csrc/gemm/ops/mxfp8_compact.cu:375 (mxfp8.cu:1456). */
+int fso_moe_fc1_swiglu(const void* hq, const void* sh, const void* w13, const void* sw13, const int32_t* blk0,
+                       const int32_t* blk_expert, int64_t num_experts, int64_t h, int64_t inter, int64_t num_blocks,
+                       int64_t rows, void* dq, void* sd, void* stream);
+
+/* Grouped FC2: dq [rows, I] x w2[e]^T -> dn bf16 [rows, H].
+ * Replaces: linear_mxfp8_grouped_compact, csrc/gemm/ops/mxfp8_compact.cu:335 (mxfp8.cu:1411). */
+int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2, const int32_t* blk0,
+                const int32_t* blk_expert, int64_t num_experts, int64_t h, int64_t inter, int64_t num_blocks,
+                int64_t rows, void* dn, void* stream);
+
+/* out[t] = bf16( sum_j w[t,j] * dn[slot_of_flat[t*topk+j]] (+ bias_scale[t] * bias[t]) ), fp32, j ascending.
+ * bias / bias_scale may be NULL. Replaces: moe_combine, csrc/gemm/ops/moe_glue.cu:2908-3016. */
+int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,
+                    const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSO_B200_H */

@@ -1,0 +1,77 @@
+"""The C-ABI library loads without a GPU, exports every symbol include/fso_b200.h declares, and refuses malformed
+arguments before touching the device (no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "fso_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fso_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(fso):
+    from fish_scales_ops_b200 import _lib
+
+    names = _declared()
+    assert "fso_gemm_mxfp8" in names and "fso_moe_combine" in names and len(names) >= 14
+    handle = ctypes.CDLL(_lib.lib_path())
+    for n in names:
+        assert hasattr(handle, n), n
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_plan(fso):
+    from fish_scales_ops_b200 import _lib, _ops
+
+    assert _lib.lib().fso_b200_version() == 1
+    p = _ops.moe_plan(8192, 2, 8)        # Mixtral bucket: 16384 pairs -> 135 blocks -> 17408 rows
+    assert (p.pairs, p.num_blocks, p.rows) == (16384, 135, 17408)
+    p = _ops.moe_plan(4096, 8, 256)      # DeepSeek-V3 bucket: 510 blocks -> 65408 rows
+    assert (p.num_blocks, p.rows) == (510, 65408)
+    p = _ops.moe_plan(1, 2, 8)
+    assert (p.num_blocks, p.rows, p.route_scratch_bytes) == (2, 384, 0)   # (2 + 127*2) // 128
+    with pytest.raises(ValueError):
+        _ops.moe_plan(4, 2, 2000)
+
+
+def test_refusals_launch_nothing(fso):
+    from fish_scales_ops_b200 import _lib
+
+    L = _lib.lib()
+    one = ctypes.c_void_p(256)   # never dereferenced: every call below is refused on its shape
+    assert L.fso_quantize_1x32(one, one, one, 4, 100, 0, None) == -1
+    assert "multiple of 128" in _lib.last_error()
+    assert L.fso_gemm_mxfp8(one, one, one, one, one, 4, 100, 128, None, 0, None) == -1
+    assert L.fso_gemm_mxfp8(ctypes.c_void_p(8), one, one, one, one, 4, 128, 128, None, 0, None) == -1
+    assert "16-byte" in _lib.last_error()
+    v = ctypes.c_int64(-1)
+    assert L.fso_gemm_mxfp8_ws_bytes(0, 128, 128, ctypes.byref(v)) == 0 and v.value == 0
+    assert L.fso_moe_combine(one, one, one, None, one, one, 4, 2, 128, None) == -1   # bias_scale without bias
+    assert L.fso_requant_bs128_to_mx(one, one, one, one, 100, 128, 0, None) == -1
+    # an empty problem is a successful no-op
+    assert L.fso_quantize_1x32(None, None, None, 0, 128, 0, None) == 0
+    assert L.fso_gemm_mxfp8(None, None, None, None, None, 0, 128, 128, None, 0, None) == 0
+
+
+def test_missing_library_fails_loudly(fso, monkeypatch):
+    from fish_scales_ops_b200 import _build, _lib
+
+    monkeypatch.setattr(_lib, "_LIB", None)
+    monkeypatch.setattr(_build, "LIB_PATH", os.path.join(ROOT, "does_not_exist.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "fish_scales_ops_b200")
+    for base, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(base, f)).read()
+                assert "oracle" not in text.replace("no oracle", ""), os.path.join(base, f)

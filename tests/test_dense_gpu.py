@@ -1,0 +1,187 @@
+"""Parity of the dense path: quantized bytes bit-exact, bf16 output within tolerance of the fp32
+dequantize-then-matmul oracle (rel. Frobenius <= 1e-2, |err| <= 2e-2 * max|ref|)."""
+import numpy as np
+import pytest
+import torch
+
+import inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_out(oracle, x, wq_np, ws_np):
+    return oracle.dense_linear(x, wq_np, ws_np)
+
+
+def test_config1_single_dense_linear(fso, oracle, device_ok):
+    """x bf16 [128, 512] ~ N(0,1), w bf16 [256, 512] ~ N(0,0.02), seeds 0 / 1."""
+    x, w = inputs.activation(128, 512, 0), inputs.weight(256, 512, 1)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    owq, ows = oracle.quantize_1x32(w)
+    assert np.array_equal(inputs.to_np_u8(weight.weight), owq)
+    assert np.array_equal(inputs.to_np_u32(weight.scale), ows)
+    xq, sx = fso.dense.quantize_activation(x.cuda())
+    oxq, oxs = oracle.quantize_1x32(x)
+    assert np.array_equal(inputs.to_np_u8(xq), oxq) and np.array_equal(inputs.to_np_u32(sx), oxs)
+    y = fso.dense.linear(x.cuda(), weight)
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (128, 256)
+    inputs.assert_close_to_oracle(y, _oracle_out(oracle, x, owq, ows), "config 1")
+    y2 = fso.dense.linear(xq, weight, x_scale=sx)
+    assert torch.equal(y, y2)
+    ref = x.float() @ w.float().t()
+    cos = torch.nn.functional.cosine_similarity(y.float().cpu().flatten(), ref.flatten(), dim=0)
+    assert cos > 0.999
+
+
+# (M, N, K): every route of the picker: swapped orientation with 16/32/64-wide token tiles, with and without
+# split-K; normal orientation with 128- and 256-wide tiles, ragged M, split-K, many tiles per CTA.
+SHAPES = [(1, 128, 128), (1, 256, 512), (7, 384, 1024), (16, 512, 4096), (17, 256, 512), (32, 1024, 1024),
+          (33, 256, 2048), (64, 640, 512), (65, 256, 512), (128, 128, 128), (128, 256, 8192), (200, 384, 640),
+          (256, 512, 256), (300, 1024, 1024), (1024, 4096, 512), (2048, 2560, 384)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_dense_shapes(fso, oracle, device_ok, m, n, k):
+    x, w = inputs.activation(m, k, m * 7 + k), inputs.weight(n, k, n * 3 + k)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    y = fso.dense.linear(x.cuda(), weight)
+    ref = _oracle_out(oracle, x, inputs.to_np_u8(weight.weight), inputs.to_np_u32(weight.scale))
+    inputs.assert_close_to_oracle(y, ref, f"M={m} N={n} K={k}")
+
+
+def test_dense_nonuniform_scales(fso, oracle, device_ok):
+    """Rows and K blocks with very different magnitudes: a wrong scale-factor placement cannot hide."""
+    m, n, k = 192, 384, 1024
+    g = inputs.gen(99)
+    x = inputs.activation(m, k, 1).float() * torch.exp2(torch.randint(-6, 7, (m, k // 32), generator=g).float()
+                                                        ).repeat_interleave(32, dim=1)
+    w = inputs.weight(n, k, 2).float() * torch.exp2(torch.randint(-6, 7, (n, k // 32), generator=g).float()
+                                                    ).repeat_interleave(32, dim=1)
+    x, w = x.to(torch.bfloat16), w.to(torch.bfloat16)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    for rows in (m, 40):
+        y = fso.dense.linear(x[:rows].cuda(), weight)
+        ref = _oracle_out(oracle, x[:rows], inputs.to_np_u8(weight.weight), inputs.to_np_u32(weight.scale))
+        inputs.assert_close_to_oracle(y, ref, f"nonuniform rows={rows}")
+
+
+def test_block_fp8_checkpoint_path(fso, oracle, device_ok):
+    n, k, m = 512, 1024, 48
+    wq, s = inputs.block_fp8_checkpoint(n, k, 5)
+    weight = fso.dense.prepare_weight(wq.cuda(), format="bsfp8", scale=s.cuda())
+    oq, osf = oracle.requant_bs128(wq, s)
+    assert np.array_equal(inputs.to_np_u8(weight.weight), oq) and np.array_equal(inputs.to_np_u32(weight.scale), osf)
+    x = inputs.activation(m, k, 6)
+    inputs.assert_close_to_oracle(fso.dense.linear(x.cuda(), weight), _oracle_out(oracle, x, oq, osf), "bsfp8")
+
+
+def test_mxfp8_checkpoint_forms(fso, oracle, device_ok):
+    n, k = 256, 512
+    w = inputs.weight(n, k, 12)
+    base = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    words = inputs.to_np_u32(base.scale)
+    rows = np.repeat(np.arange(n), k // 128)
+    kps = np.tile(np.arange(k // 128), n)
+    u8 = torch.from_numpy(words[oracle.sf_word_index(rows, kps, k)].reshape(n, k // 128).view(np.uint8).copy())
+    from_bytes = fso.dense.prepare_weight(base.weight, format="mxfp8", scale=u8.view(n, k // 32).cuda())
+    assert torch.equal(from_bytes.scale, base.scale) and from_bytes.weight.data_ptr() == base.weight.data_ptr()
+    from_words = fso.dense.prepare_weight(base.weight, format="mxfp8", scale=base.scale)
+    assert torch.equal(from_words.scale, base.scale)
+
+
+def test_leading_dims_empty_and_quantized(fso, oracle, device_ok):
+    w = inputs.weight(256, 256, 3)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    x = inputs.activation(6 * 5, 256, 4).view(6, 5, 256).cuda()
+    y = fso.dense.linear(x, weight)
+    assert tuple(y.shape) == (6, 5, 256)
+    assert torch.equal(y.view(30, 256), fso.dense.linear(x.view(30, 256), weight))
+    assert tuple(fso.dense.linear(x[:0], weight).shape) == (0, 5, 256)
+    q, s = fso.dense.linear_quantized(x.view(30, 256), weight)
+    q2, s2 = fso.dense.quantize_activation(y.view(30, 256))
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2)
+    # a bf16 x at a 2-byte offset is copied inside the op and gives the same bytes
+    buf = torch.zeros(30 * 256 + 1, dtype=torch.bfloat16, device="cuda")
+    buf[1:] = x.reshape(-1)
+    assert torch.equal(fso.dense.linear(buf[1:].view(30, 256), weight), y.view(30, 256))
+
+
+def test_refusals_before_launch(fso, device_ok):
+    w = inputs.weight(256, 256, 3).cuda()
+    weight = fso.dense.prepare_weight(w, format="mxfp8")
+    x = inputs.activation(8, 256, 4).cuda()
+    with pytest.raises(ValueError):
+        fso.dense.prepare_weight(w[:, :100], format="mxfp8")
+    with pytest.raises(ValueError):
+        fso.dense.prepare_weight(w[:100], format="mxfp8")
+    with pytest.raises(ValueError):
+        fso.dense.prepare_weight(w, format="mxfp9")
+    with pytest.raises(NotImplementedError):
+        fso.dense.prepare_weight(w, format="nvfp4")
+    with pytest.raises(ValueError):
+        fso.dense.prepare_weight(w, format="mxfp8", scale=torch.ones(2, 2, device="cuda"))
+    with pytest.raises(TypeError):
+        fso.dense.linear(x, w)
+    with pytest.raises(ValueError):
+        fso.dense.linear(x[:, :128], weight)
+    with pytest.raises(ValueError):
+        fso.dense.linear(x.float(), weight)
+    xq, sx = fso.dense.quantize_activation(x)
+    with pytest.raises(ValueError):
+        fso.dense.linear(xq, weight)
+    with pytest.raises(ValueError):
+        fso.dense.linear(x, weight, x_scale=sx)
+    with pytest.raises(ValueError):
+        fso.dense.linear(xq, weight, x_scale=sx[:-1])
+    with pytest.raises(NotImplementedError):
+        fso.dense.linear(x, weight, bias=torch.zeros(256, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        fso.dense.linear(x, weight, activation="nope")
+    with pytest.raises(NotImplementedError):
+        fso.dense.linear(x, weight, activation="silu")
+    assert fso.dense.supported("mxfp8") and fso.dense.supported("bsfp8") and not fso.dense.supported("nvfp4")
+    assert fso.dense.activation_contract()["format"] == "mxfp8_1x32"
+    torch.cuda.synchronize()   # the context is intact after every refusal
+    fso.dense.linear(x, weight)
+
+
+def test_cuda_graph_capture_and_no_sync(fso, oracle, device_ok):
+    """Capture after one eager call, NaN-filled replay buffers, replay == eager after rewriting x in place; the call
+    never synchronizes (python side of tests/gemm/unit/test_cuda_graph.py:33-80 of the reference)."""
+    for m in (16, 384):
+        w = inputs.weight(512, 1024, 21)
+        weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+        x = inputs.activation(m, 1024, 22).cuda()
+        eager = fso.dense.linear(x, weight)
+        torch.cuda.synchronize()
+        torch.cuda.set_sync_debug_mode("error")
+        try:
+            fso.dense.linear(x, weight)
+        finally:
+            torch.cuda.set_sync_debug_mode("default")
+        static_x = x.clone()
+        graph = torch.cuda.CUDAGraph()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            fso.dense.linear(static_x, weight)
+            with torch.cuda.graph(graph, stream=stream):
+                out = fso.dense.linear(static_x, weight)
+        torch.cuda.current_stream().wait_stream(stream)
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+        x2 = inputs.activation(m, 1024, 23).cuda()
+        static_x.copy_(x2)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, fso.dense.linear(x2, weight))
+
+
+def test_run_to_run_identical_including_split_k(fso, device_ok):
+    w = inputs.weight(256, 8192, 1)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    for m in (4, 128):
+        x = inputs.activation(m, 8192, 2).cuda()
+        assert torch.equal(fso.dense.linear(x, weight), fso.dense.linear(x, weight))

@@ -1,0 +1,145 @@
+"""The CPU checker against the reference: its own header compiled on the host (oracle/_ref, where present) and the
+golden vectors generated from it (tests/golden/quantize_1x32.npz)."""
+import ctypes
+import hashlib
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import inputs
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quantize_1x32.npz")
+
+
+def _sha(q, sf):
+    return hashlib.sha256(q.tobytes() + sf.tobytes()).hexdigest()
+
+
+def test_golden_edge_vector(oracle):
+    g = np.load(GOLDEN)
+    edge = inputs.edge_activation()
+    assert np.array_equal(oracle.bf16_bits(edge), g["edge_x_bits"]), "the edge input generator drifted"
+    q, sf = oracle.quantize_1x32(edge)
+    assert np.array_equal(q, g["edge_q"])
+    assert np.array_equal(sf, g["edge_sf"])
+    # padded rows 130..255 of the second 128-row block: zero words
+    rows = np.arange(130, 256)
+    for kp in range(2):
+        assert not sf[oracle.sf_word_index(rows, np.full_like(rows, kp), 256)].any()
+
+
+def test_golden_config1(oracle):
+    g = np.load(GOLDEN)
+    xq, xs = oracle.quantize_1x32(inputs.activation(128, 512, 0))
+    wq, ws = oracle.quantize_1x32(inputs.weight(256, 512, 1))
+    assert _sha(xq, xs) == str(g["cfg1_x_sha"])
+    assert _sha(wq, ws) == str(g["cfg1_w_sha"])
+    assert np.array_equal(xq[:8], g["cfg1_x_q_head"])
+    assert np.array_equal(xs, g["cfg1_x_sf"])
+
+
+def test_known_bytes_of_the_rule(oracle):
+    # amax -> scale byte examples: 0.5 -> 118, 448 -> 127, 896 -> 128, 1e-10 (the floor) -> 85
+    L = oracle.lib()
+    for amax, want in ((0.5, 118), (448.0, 127), (896.0, 128), (1e-10, 85)):
+        qs = ctypes.c_float()
+        assert L.orc_e8m0_from_amax(ctypes.c_float(amax), ctypes.byref(qs)) == want
+        assert L.orc_e8m0_from_amax_int(ctypes.c_float(amax), ctypes.byref(qs)) == want
+
+
+def test_integer_rule_equals_divide_rule_for_every_bf16_amax(oracle):
+    L = oracle.lib()
+    floor = np.float32(1e-10)
+    vals = [floor] + [v for v in (np.arange(1, 0x7F80, dtype=np.uint32) << 16).view(np.float32) if v >= floor]
+    for v in vals:
+        a, b = ctypes.c_float(), ctypes.c_float()
+        x = L.orc_e8m0_from_amax(ctypes.c_float(v), ctypes.byref(a))
+        y = L.orc_e8m0_from_amax_int(ctypes.c_float(v), ctypes.byref(b))
+        assert x == y and np.float32(a.value).tobytes() == np.float32(b.value).tobytes(), float(v)
+
+
+def test_restatement_matches_reference_header(oracle):
+    R = oracle.ref_lib()
+    if R is None:
+        pytest.skip("oracle/_ref is not built here (no reference tree); the golden vectors pin the same bytes")
+    L = oracle.lib()
+    assert R.ref_contract_version() == 1
+    rng = np.random.default_rng(7)
+    xs = np.concatenate([rng.standard_normal(20000).astype(np.float32) * s for s in (1, 30, 500, 1e-2, 1e-4)])
+    for v in xs[::3]:
+        assert L.orc_e4m3_from_float(ctypes.c_float(v)) == R.ref_e4m3_from_float(ctypes.c_float(v)), float(v)
+    for m, kp, k in ((0, 0, 128), (37, 1, 512), (129, 3, 512), (1000, 7, 1024)):
+        assert L.orc_sf_word_index(m, kp, k) == R.ref_sf_word_index_sm100(m, kp, k)
+    x = torch.randn(257, 384, generator=inputs.gen(3)).to(torch.bfloat16)
+    q, s = oracle.quantize_1x32(x)
+    q2, s2 = oracle.ref_quantize_1x32(x)
+    assert np.array_equal(q, q2) and np.array_equal(s, s2)
+
+
+def test_interleave_is_a_row_permutation(oracle):
+    e, i, k = 2, 128, 256
+    w = inputs.weight(e * 2 * i, k, 5)
+    q, s = oracle.quantize_1x32(w)
+    qi, si = oracle.quantize_1x32(w, interleave_i=i)
+    for g in range(e):
+        for r in range(2 * i):
+            src = g * 2 * i + (i + r // 2 if r & 1 else r // 2)
+            dst = g * 2 * i + r
+            assert np.array_equal(qi[dst], q[src])
+            for kp in range(k // 128):
+                assert si[oracle.sf_word_index(np.array(dst), np.array(kp), k)] == \
+                    s[oracle.sf_word_index(np.array(src), np.array(kp), k)]
+
+
+def test_pack_ue8m0_matches_quantizer_words(oracle):
+    # bytes [N, K/32] taken from the quantizer's own words must pack back to the same words
+    w = inputs.weight(256, 512, 11)
+    _, s = oracle.quantize_1x32(w)
+    n, k = 256, 512
+    rows = np.repeat(np.arange(n), k // 128)
+    kps = np.tile(np.arange(k // 128), n)
+    words = s[oracle.sf_word_index(rows, kps, k)].reshape(n, k // 128)
+    bytes_ = words.view(np.uint8).reshape(1, n, k // 32)
+    assert np.array_equal(oracle.pack_ue8m0(bytes_)[0], s)
+
+
+def test_requant_is_dequant_then_quantize(oracle):
+    wq, s = inputs.block_fp8_checkpoint(256, 256, 21)
+    q, sf = oracle.requant_bs128(wq, s)
+    deq = (wq.to(torch.float32).view(2, 128, 2, 128) * s.view(2, 1, 2, 1)).view(256, 256).to(torch.bfloat16)
+    q2, sf2 = oracle.quantize_1x32(deq)
+    assert np.array_equal(q, q2) and np.array_equal(sf, sf2)
+
+
+def test_route_contract(oracle):
+    # the contract of tests/gemm/unit/test_moe_routing_compact.py:98-195 of the reference, on the canonical order
+    ids, _ = inputs.routing(300, 16, 4, 9)
+    ids = ids.clone()
+    ids[5, 1] = -1
+    ids[6, 0] = 16
+    nb = max(1, (1200 + 127 * 16) // 128)
+    mm, b0, sl, be = oracle.route(ids, 16, nb)
+    flat = ids.reshape(-1).numpy()
+    valid = (flat >= 0) & (flat < 16)
+    assert np.array_equal(mm, np.bincount(flat[valid], minlength=16))
+    assert np.array_equal(b0, np.concatenate([[0], np.cumsum((mm + 127) // 128)]))
+    assert (sl[~valid] == -1).all()
+    live = sl[valid]
+    assert len(set(live.tolist())) == live.size
+    for e in range(16):
+        mine = np.nonzero(flat == e)[0]
+        assert np.array_equal(sl[mine], b0[e] * 128 + np.arange(mine.size))
+        assert (be[b0[e]:b0[e + 1]] == e).all()
+    assert (be[b0[16]:] == -1).all()
+
+
+def test_dense_oracle_tracks_bf16_masters(oracle):
+    x = inputs.activation(32, 512, 0)
+    w = inputs.weight(64, 512, 1)
+    wq, ws = oracle.quantize_1x32(w)
+    y = oracle.dense_linear(x, wq, ws)
+    ref = x.float() @ w.float().t()
+    cos = torch.nn.functional.cosine_similarity(y.flatten(), ref.flatten(), dim=0)
+    assert cos > 0.999
