@@ -43,6 +43,7 @@ struct GemmParams {
     int ldo;                   // leading dimension of out / ws rows, in elements
     int num_experts;
     int group_a;               // raster: tiles of A walked together before B advances
+    int out_align32;           // the output base is 32-byte aligned (256-bit stores are usable)
     int64_t out_rows;          // rows of the output (row stride of one split's partial = out_rows * ldo)
 };
 
@@ -304,6 +305,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 + static_cast<uint32_t>(acc * BN);
             int const a_row = c.a_tile * C::kBM + quarter * 32 + lane;   // this thread's row of the MMA-M operand
             int const b_row0 = c.b_tile * BN;
+            bool released = false;
 
             if constexpr (EPI == EPI_SWIGLU) {
                 // interleaved (gate, up) columns -> 64 outputs per warp = two 1x32 blocks per row
@@ -350,8 +352,53 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         + sf_word_index(a_row, c.b_tile, inter / 128) * 4 + half * 2;
                     *reinterpret_cast<uint16_t*>(w) = static_cast<uint16_t>(bytes2);
                 }
+            } else if constexpr (!kSwap && EPI == EPI_BF16) {
+                // row = output row, columns = output columns. The accumulator slice is drained into packed bf16
+                // registers first and handed back to the MMA issuer; the global stores then overlap the next tile.
+                constexpr int kPacked = kColsPerWarp / 2;
+                uint32_t packed[kPacked];
+#pragma unroll
+                for (int c0 = 0; c0 < kColsPerWarp; c0 += 64) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(t_row + half * kColsPerWarp + c0, r0);
+                    if (c0 + 32 < kColsPerWarp) tmem_ld_32x32(t_row + half * kColsPerWarp + c0 + 32, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        packed[c0 / 2 + j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                    if (c0 + 32 < kColsPerWarp) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            packed[c0 / 2 + 16 + j]
+                                = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                released = true;
+                if (a_row < p.rows_a) {
+                    __nv_bfloat16* const orow = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(a_row) * p.ldo
+                        + b_row0 + half * kColsPerWarp;
+#pragma unroll
+                    for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+                        if (b_row0 + half * kColsPerWarp + c0 < p.rows_b) {
+                            uint32_t const* v = &packed[c0 / 2];
+                            if (p.out_align32) {
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                             ::"l"(orow + c0), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]),
+                                             "r"(v[5]), "r"(v[6]), "r"(v[7])
+                                             : "memory");
+                            } else {
+                                uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+                                dst[0] = make_uint4(v[0], v[1], v[2], v[3]);
+                                dst[1] = make_uint4(v[4], v[5], v[6], v[7]);
+                            }
+                        }
+                    }
+                }
             } else if constexpr (!kSwap) {
-                // row = output row, columns = output columns
+                // split-K partial, normal orientation: fp32 rows straight from tensor memory
 #pragma unroll 1
                 for (int c0 = half * kColsPerWarp; c0 < (half + 1) * kColsPerWarp; c0 += 32) {
                     uint32_t r[32];
@@ -359,25 +406,11 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     tmem_ld_wait();
                     int const col = b_row0 + c0;
                     if (a_row < p.rows_a && col < p.rows_b) {
-                        if constexpr (EPI == EPI_BF16) {
-                            uint4* dst = reinterpret_cast<uint4*>(
-                                static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(a_row) * p.ldo + col);
+                        uint4* dst = reinterpret_cast<uint4*>(p.ws + static_cast<int64_t>(c.split) * p.out_rows * p.ldo
+                            + static_cast<int64_t>(a_row) * p.ldo + col);
 #pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 o;
-                                o.x = pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
-                                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                                dst[v] = o;
-                            }
-                        } else {
-                            uint4* dst = reinterpret_cast<uint4*>(p.ws + static_cast<int64_t>(c.split) * p.out_rows * p.ldo
-                                + static_cast<int64_t>(a_row) * p.ldo + col);
-#pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                dst[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                        }
+                        for (int v = 0; v < 8; ++v)
+                            dst[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
                     }
                 }
             } else {
@@ -401,9 +434,11 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (!released) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+            }
             if (++acc == C::kAccStages) {
                 acc = 0;
                 acc_phase ^= 1u;

@@ -71,7 +71,7 @@ inline void pick_splits(int64_t tiles, int kb, int sms, int min_kb, int* splits,
 {
     int best_s = 1;
     double best = wave_efficiency(tiles, sms);
-    if (tiles < sms) {
+    if (tiles * 2 <= sms) {
         for (int s = 2; s <= 16; ++s) {
             int const per = (kb + s - 1) / s;
             if (per < min_kb) break;
@@ -161,6 +161,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     p.out = d;
     p.ws = static_cast<float*>(ws);
     p.out_rows = m;
+    p.out_align32 = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 ? 1 : 0;
     int rc;
     if (pl.swap) {
         if ((rc = make_operand_map(&ta, w, n, k, 128)) != 0) return rc;
@@ -241,6 +242,7 @@ inline int launch_grouped(const void* a, const void* sfa, const void* weight, co
     p.num_experts = static_cast<int>(num_experts);
     p.group_a = 16;
     p.out_rows = rows;
+    p.out_align32 = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 ? 1 : 0;
     int64_t const items = static_cast<int64_t>(p.tiles_a) * p.tiles_b;
     int const grid = static_cast<int>(items < sms ? items : sms);
     if (swiglu) return launch_gemm_inst<256, EPI_SWIGLU, false, true>(ta, tb, p, grid, stream);
