@@ -25,6 +25,7 @@ SIGNATURES = {
     "fso_gemm_mxfp8": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_i64, _c_p],
     "fso_moe_plan_make": [_c_i64, _c_i64, _c_i64, _c_p],
     "fso_moe_route": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_p],
+    "fso_moe_route_noalloc": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p],
     "fso_moe_gather_quant": [_c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p],
     "fso_moe_fc1_swiglu": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p,
                            _c_p],

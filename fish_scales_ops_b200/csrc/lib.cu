@@ -188,6 +188,80 @@ int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_
     return launch_status("route kernels");
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Routing for callers that must not allocate.
+//
+// Some callers of this library cannot hand it scratch memory at the moment they need a routing: a serving engine
+// that has given every free byte of the device to its own pool and forbids cudaMalloc in the forward pass, or a
+// plugin that runs where an allocation would stall the stream. For them this entry point keeps the per-segment
+// counts of the multi-segment routing in an array that is part of the library image itself (256 KiB, resident on
+// every GPU that loads the library until the process exits). It calls no cudaMalloc / cudaFree and no allocating
+// library routine; inputs and outputs are still the caller's.
+//
+// The array's name is only a host-side stand-in in host code, not a device address, so the device address is looked
+// up once per device with cudaGetSymbolAddress (with that device current) and handed to the kernels. That lookup
+// happens in the first call made on a device; make that first call outside any stream capture.
+// Limits: tokens * topk <= kRouteStaticMaxPairs; larger calls are refused. The array is shared by every call and
+// keeps the previous call's contents; the kernels overwrite every word they later read, so nothing needs clearing,
+// but two calls that overlap on the GPU (different streams) race on it: serialize them.
+constexpr int64_t kRouteStaticMaxPairs = 65536;
+constexpr int64_t kRouteStaticWords = (kRouteStaticMaxPairs / kRouteSeg) * 1024;   // 64 segments x 1024 experts
+static __device__ __align__(256) int32_t g_route_static_scratch[kRouteStaticWords];
+
+static int route_static_scratch_ptr(int32_t** out)
+{
+    static std::mutex mu;
+    static int32_t* ptrs[64] = {};
+    int dev = 0;
+    FSO_CUDA(cudaGetDevice(&dev));
+    FSO_REQUIRE(dev >= 0 && dev < 64, "fso_moe_route_noalloc: device index %d is beyond the 64 this entry point tracks", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        FSO_CUDA(cudaGetSymbolAddress(&p, g_route_static_scratch));
+        ptrs[dev] = static_cast<int32_t*>(p);
+    }
+    *out = ptrs[dev];
+    return 0;
+}
+
+int fso_moe_route_noalloc(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_experts, int64_t num_blocks,
+    int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* stream)
+{
+    fso_moe_plan pl;
+    int const rc = fso_moe_plan_make(tokens, topk, num_experts, &pl);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(pl.pairs <= kRouteStaticMaxPairs,
+        "fso_moe_route_noalloc: tokens * topk = %lld exceeds the %lld pairs its built-in scratch covers; use "
+        "fso_moe_route with caller scratch", static_cast<long long>(pl.pairs), static_cast<long long>(kRouteStaticMaxPairs));
+    FSO_REQUIRE(num_blocks >= pl.num_blocks, "fso_moe_route_noalloc: num_blocks = %lld is below the bound %lld of this call",
+        static_cast<long long>(num_blocks), static_cast<long long>(pl.num_blocks));
+    FSO_REQUIRE(masked_m && blk0 && blk_expert && (pl.pairs == 0 || (ids && slot_of_flat)),
+        "fso_moe_route_noalloc: NULL pointer");
+    cudaStream_t const st = as_stream(stream);
+    int const e = static_cast<int>(num_experts), nb = static_cast<int>(num_blocks), pairs = static_cast<int>(pl.pairs);
+    size_t const smem = static_cast<size_t>(64) * e;
+    if (pairs <= kRouteSeg) {
+        route_small_kernel<<<1, kRouteSeg, smem, st>>>(ids, pairs, e, nb, masked_m, blk0, slot_of_flat, blk_expert);
+        return launch_status("route_small_kernel");
+    }
+    int32_t* seg = nullptr;
+    int const rp = route_static_scratch_ptr(&seg);
+    if (rp != 0) return rp;
+    int const segs = (pairs + kRouteSeg - 1) / kRouteSeg;
+    static std::atomic<uint64_t> done_count{0}, done_place{0};
+    if (smem > 48 * 1024) {
+        int r2 = ensure_smem_attr(route_count_kernel, static_cast<int>(smem), done_count);
+        if (r2 != 0) return r2;
+        r2 = ensure_smem_attr(route_place_kernel, static_cast<int>(smem), done_place);
+        if (r2 != 0) return r2;
+    }
+    route_count_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg);
+    route_scan_kernel<<<1, kRouteSeg, 0, st>>>(seg, segs, e, nb, masked_m, blk0, blk_expert);
+    route_place_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg, blk0, slot_of_flat);
+    return launch_status("route kernels (built-in scratch)");
+}
+
 int fso_moe_gather_quant(const void* hidden, const int32_t* slot_of_flat, int64_t tokens, int64_t topk, int64_t h,
     int64_t rows, void* hq, void* sh, void* stream)
 {

@@ -85,6 +85,16 @@ int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_
                   int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* scratch,
                   int64_t scratch_bytes, void* stream);
 
+/* fso_moe_route for callers that cannot pass scratch memory and must not allocate (an engine that owns all device
+ * memory and forbids allocation in its forward pass, code running where cudaMalloc would stall the stream): the
+ * scratch is a 256 KiB array inside the library image, resident on every GPU that loads the library. Same outputs,
+ * bit for bit, as fso_moe_route. tokens * topk <= 65536, otherwise FSO_ERR_INVALID. The first call on a device looks
+ * up the array's device address (make it outside stream capture); calls share the array, so calls that overlap on
+ * the GPU race and must be serialized. Allocates nothing. No counterpart in the reference (its routing op allocates
+ * through the torch caching allocator). */
+int fso_moe_route_noalloc(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_experts, int64_t num_blocks,
+                          int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* stream);
+
 /* Row gather + 1x32 quantize into the compact buffers: row slot_of_flat[i] of hq / sh takes token i / topk.
  * hq e4m3 [rows, H], sh scale words of a [rows, H] tensor. Rows no pair maps to are not written.
  * Replaces: quantize_1x32_grouped_gather_out, csrc/gemm/ops/mxfp8_compact.cu:206. */
