@@ -273,6 +273,7 @@ int fso_moe_gather_quant(const void* hidden, const int32_t* slot_of_flat, int64_
         "fso_moe_gather_quant: hidden and hq must be 16-byte aligned");
     constexpr int kUnroll = 2;
     int const kb = static_cast<int>(h / 128);
+    FSO_REQUIRE(tokens * kb < (1ll << 31) - 4096, "fso_moe_gather_quant: tokens * H/128 is beyond the kernel's index range");
     int64_t const halves = (tokens * kb + kUnroll - 1) / kUnroll;
     int64_t const blocks = (halves * 16 + 255) / 256;
     gather_quant_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
@@ -329,6 +330,7 @@ int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* to
     FSO_REQUIRE(bias != nullptr || bias_scale == nullptr, "fso_moe_combine: bias_scale scales bias and needs it");
     int const h8 = static_cast<int>(h / 8);
     int64_t const total = tokens * h8;
+    FSO_REQUIRE(total < (1ll << 31) - 4096, "fso_moe_combine: tokens * H/8 is beyond the kernel's index range");
     combine_kernel<8><<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
         static_cast<const uint4*>(dn), slot_of_flat, topk_w, static_cast<const uint4*>(bias), bias_scale,
         static_cast<uint4*>(out), tokens, static_cast<int>(topk), h8);

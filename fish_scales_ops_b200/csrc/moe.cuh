@@ -168,26 +168,27 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(const uint4* __restri
     const int32_t* __restrict__ slot_of_flat, int64_t tokens, int topk, int kb, uint2* __restrict__ hq,
     uint32_t* __restrict__ sh)
 {
-    int const sub = threadIdx.x & 15;
-    int64_t const half = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-    int64_t const total = tokens * kb;
+    // 32-bit index arithmetic (the launcher refuses more than 2^31 chunks)
+    uint32_t const sub = threadIdx.x & 15;
+    uint32_t const half = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    uint32_t const total = static_cast<uint32_t>(tokens) * static_cast<uint32_t>(kb);
     uint4 v[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-        int64_t const c = half * kUnroll + u;
-        v[u] = c < total ? __ldg(hidden + c * 16 + sub) : make_uint4(0, 0, 0, 0);
+        uint32_t const c = half * kUnroll + u;
+        v[u] = c < total ? __ldg(hidden + static_cast<size_t>(c) * 16 + sub) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-        int64_t const c = half * kUnroll + u;
+        uint32_t const c = half * kUnroll + u;
         uint2 codes;
         uint32_t const byte = quant8_shared4(v[u], codes);
         uint32_t const word = word_from_16lanes(byte, sub);
         if (c < total) {
-            int64_t const t = c / kb;
+            uint32_t const t = c / static_cast<uint32_t>(kb);
             int const kp = static_cast<int>(c - t * kb);
             for (int j = 0; j < topk; ++j) {
-                int const slot = __ldg(slot_of_flat + t * topk + j);
+                int const slot = __ldg(slot_of_flat + static_cast<size_t>(t) * topk + j);
                 if (slot >= 0) {
                     hq[(static_cast<int64_t>(slot) * kb + kp) * 16 + sub] = codes;
                     if (sub == 0) sh[sf_word_index(slot, kp, kb)] = word;
@@ -206,10 +207,12 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
     const int32_t* __restrict__ slot_of_flat, const float* __restrict__ topk_w, const uint4* __restrict__ bias,
     const float* __restrict__ bias_scale, uint4* __restrict__ out, int64_t tokens, int topk, int h8)
 {
-    int64_t const idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= tokens * h8) return;
-    int64_t const t = idx / h8;
-    int const c = static_cast<int>(idx - t * h8);
+    // 32-bit index arithmetic (the launcher refuses tokens * H/8 >= 2^31)
+    uint32_t const idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<uint32_t>(tokens) * static_cast<uint32_t>(h8)) return;
+    uint32_t const t32 = idx / static_cast<uint32_t>(h8);
+    int const c = static_cast<int>(idx - t32 * h8);
+    int64_t const t = t32;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     auto fma_row = [&](uint4 const& raw, float w) {
         uint32_t const ws[4] = {raw.x, raw.y, raw.z, raw.w};

@@ -90,41 +90,46 @@ __device__ __forceinline__ uint32_t word_from_16lanes(uint32_t byte, int sub16)
 // kUnroll independent 16-byte loads per thread are in flight. Rows in [m, m_pad) only get their zero words.
 template <int kUnroll>
 __global__ void __launch_bounds__(256) quantize_1x32_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
-    uint32_t* __restrict__ sf, int64_t m, int64_t m_pad, int kb, int64_t interleave_i)
+    uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i)
 {
-    int const sub = threadIdx.x & 15;
-    int64_t const half = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-    int64_t const total = m_pad * kb;
-    int64_t const c0 = half * kUnroll;
+    // 32-bit index arithmetic throughout (the launcher refuses more than 2^31 chunks): one division per thread.
+    uint32_t const sub = threadIdx.x & 15;
+    uint32_t const half = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    uint32_t const total = m_pad * kb;
+    uint32_t const c0 = half * kUnroll;
+    uint32_t row0 = c0 / kb;
+    uint32_t kp0 = c0 - row0 * kb;
 
     uint4 v[kUnroll];
-    int64_t row[kUnroll];
-    int kp[kUnroll];
+    uint32_t row[kUnroll];
+    uint32_t kp[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-        int64_t const c = c0 + u;
-        row[u] = c / kb;
-        kp[u] = static_cast<int>(c - row[u] * kb);
+        row[u] = row0;
+        kp[u] = kp0;
+        if (++kp0 == kb) {
+            kp0 = 0;
+            ++row0;
+        }
         v[u] = make_uint4(0, 0, 0, 0);
-        if (c < total && row[u] < m) {
-            int64_t src = row[u];
+        if (c0 + u < total && row[u] < m) {
+            uint32_t src = row[u];
             if (interleave_i > 0) {
-                int64_t const two_i = 2 * interleave_i;
-                int64_t const g = src / two_i, o = src - g * two_i;
+                uint32_t const two_i = 2 * interleave_i;
+                uint32_t const g = src / two_i, o = src - g * two_i;
                 src = g * two_i + ((o & 1) ? interleave_i + (o >> 1) : (o >> 1));
             }
-            v[u] = __ldg(x + (src * kb + kp[u]) * 16 + sub);
+            v[u] = __ldg(x + (static_cast<size_t>(src) * kb + kp[u]) * 16 + sub);
         }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-        int64_t const c = c0 + u;
         uint2 codes;
         uint32_t const byte = quant8_shared4(v[u], codes);
         uint32_t const word = word_from_16lanes(byte, sub);
-        if (c < total) {
+        if (c0 + u < total) {
             bool const live = row[u] < m;
-            if (live) q[(row[u] * kb + kp[u]) * 16 + sub] = codes;
+            if (live) q[(static_cast<size_t>(row[u]) * kb + kp[u]) * 16 + sub] = codes;
             if (sub == 0) sf[sf_word_index(row[u], kp[u], kb)] = live ? word : 0u;
         }
     }
@@ -138,8 +143,14 @@ inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int
     int const kb = static_cast<int>(k / 128);
     int64_t const halves = (m_pad * kb + kUnroll - 1) / kUnroll;
     int64_t const blocks = (halves * 16 + 255) / 256;
+    if (m_pad * kb >= (1ll << 31) - 4096 || m_pad >= (1ll << 31)) {
+        set_error("fso_quantize_1x32: %lld x %lld is beyond the kernel's 2^31-chunk index range; split the call by rows",
+            static_cast<long long>(m), static_cast<long long>(k));
+        return FSO_ERR_INVALID;
+    }
     quantize_1x32_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        static_cast<const uint4*>(x), static_cast<uint2*>(q), static_cast<uint32_t*>(sf), m, m_pad, kb, interleave_i);
+        static_cast<const uint4*>(x), static_cast<uint2*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(m),
+        static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i));
     return launch_status("fso_quantize_1x32");
 }
 

@@ -1,0 +1,133 @@
+"""Multi-GPU use of the path, one process per GPU over ``torch.distributed``.
+
+The reference has no communication code: tensor- and expert-parallel callers shard the weights themselves and
+reduce the partial results (docs/guide.md:139-141, python/fish_scales_ops/moe/__init__.py:733-739). Two helpers
+cover the two ways the path shards:
+
+* dense linears split along N (column parallel): every rank prepares its own rows of the weight and computes its
+  own output columns from the same activation; there is no exchange step, so nothing here calls a collective;
+* MoE layers split by expert (expert parallel): rank r owns experts ``[r*E/G, (r+1)*E/G)``. Each token row is
+  sent once to every rank that owns at least one of its top-k experts (all-to-all-v dispatch), the local layer runs
+  with the ids of other ranks' experts rewritten to -1 (the layer skips them at no cost and returns a partial sum),
+  the partial rows travel back (all-to-all-v combine) and the source rank adds them in rank order in fp32.
+
+Kernels only ever read this GPU's memory: rows arrive through NCCL before any kernel touches them.
+"""
+import dataclasses
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def column_shard(n: int, world: int, rank: int):
+    """Rows ``[r0, r1)`` of an ``[N, K]`` weight that rank ``rank`` of ``world`` serves (N-split). Every shard must
+    keep ``N / world`` a multiple of 128, which the MXFP8 GEMM requires."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"column_shard: rank {rank} of world {world}")
+    if n % world != 0 or (n // world) % 128 != 0:
+        raise ValueError(f"column_shard: N = {n} split {world} ways leaves {n / world:g} rows per rank, which is not "
+                         f"a multiple of 128")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def expert_shard(num_experts: int, world: int, rank: int):
+    """Experts ``[e0, e1)`` owned by ``rank`` under expert parallelism."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"expert_shard: rank {rank} of world {world}")
+    if num_experts % world != 0:
+        raise ValueError(f"expert_shard: {num_experts} experts do not split evenly over {world} ranks")
+    per = num_experts // world
+    return rank * per, (rank + 1) * per
+
+
+@dataclasses.dataclass
+class DispatchPlan:
+    """What one rank sends where, for one batch. Row i of the send buffer is token ``send_token[i]``; the rows for
+    destination rank r are the contiguous range given by ``send_counts``."""
+
+    send_token: torch.Tensor          # int64 [S]: source token of each sent row, grouped by destination rank
+    send_counts: list                 # python ints [G]
+    recv_counts: list                 # python ints [G]
+
+
+def build_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
+    """Which token goes to which rank: a token is sent to rank r when at least one of its top-k ids lies in r's
+    expert range (ids outside ``[0, E_global)`` belong to nobody). One small count exchange tells every rank how many
+    rows it will receive; this is the only host read in the exchange."""
+    t = int(topk_ids.shape[0])
+    ids = topk_ids.to(torch.int64)
+    valid = (ids >= 0) & (ids < experts_per_rank * world)
+    owner = torch.where(valid, ids // experts_per_rank, torch.full_like(ids, -1))
+    ranks = torch.arange(world, device=ids.device, dtype=torch.int64)
+    needs = (owner.unsqueeze(-1) == ranks).any(dim=1)                      # [T, G]
+    # rows grouped by destination rank, tokens ascending inside a group (deterministic)
+    dest, tok = torch.nonzero(needs.t().contiguous(), as_tuple=True)        # sorted by rank, then token
+    counts = needs.sum(dim=0).to(torch.int64)
+    recv = torch.empty_like(counts)
+    dist.all_to_all_single(recv, counts, group=group)
+    del dest, t
+    return DispatchPlan(tok, [int(v) for v in counts.tolist()], [int(v) for v in recv.tolist()])
+
+
+def _a2a_rows(rows: torch.Tensor, in_counts, out_counts, group) -> torch.Tensor:
+    out = rows.new_empty((sum(out_counts),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(out_counts),
+                           input_split_sizes=list(in_counts), group=group)
+    return out
+
+
+def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *,
+                          num_experts_global: int, group=None,
+                          layer_fn: Optional[Callable] = None) -> torch.Tensor:
+    """One MoE layer under expert parallelism: ``hidden`` bf16 ``[T, H]`` are this rank's tokens, ``topk_ids``
+    ``[T, k]`` are GLOBAL expert ids, ``experts`` holds this rank's local experts. Returns the full result
+    ``[T, H]`` for this rank's tokens (bf16), equal to the single-GPU layer over all experts up to the rounding of
+    the partial sums.
+
+    ``layer_fn(hidden, experts, local_ids, weights)`` defaults to :func:`fish_scales_ops_b200.moe.layer`; the tests
+    of the exchange logic pass a CPU stand-in."""
+    if layer_fn is None:
+        from . import moe
+
+        layer_fn = moe.layer
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if num_experts_global % world != 0:
+        raise ValueError(f"expert_parallel_layer: {num_experts_global} experts over {world} ranks")
+    per = num_experts_global // world
+    t, h = int(hidden.shape[0]), int(hidden.shape[1])
+    plan = build_dispatch(topk_ids, per, world, group)
+
+    # dispatch: token rows, their ids and their weights
+    send_rows = hidden.index_select(0, plan.send_token)
+    send_ids = topk_ids.to(torch.int32).index_select(0, plan.send_token)
+    send_w = topk_w.to(torch.float32).index_select(0, plan.send_token)
+    recv_rows = _a2a_rows(send_rows, plan.send_counts, plan.recv_counts, group)
+    recv_ids = _a2a_rows(send_ids, plan.send_counts, plan.recv_counts, group)
+    recv_w = _a2a_rows(send_w, plan.send_counts, plan.recv_counts, group)
+
+    # local experts only: everybody else's ids become -1, mine become local indices
+    lo = rank * per
+    mine = (recv_ids >= lo) & (recv_ids < lo + per)
+    local_ids = torch.where(mine, recv_ids - lo, torch.full_like(recv_ids, -1))
+    partial = layer_fn(recv_rows, experts, local_ids, recv_w)
+
+    # combine: partial rows go back to their source rank, which adds them in rank order (fp32, one rounding)
+    back = _a2a_rows(partial, plan.recv_counts, plan.send_counts, group)
+    out = torch.zeros((t, h), dtype=torch.float32, device=hidden.device)
+    start = 0
+    for r in range(world):
+        n = plan.send_counts[r]
+        if n:
+            out.index_add_(0, plan.send_token[start:start + n], back[start:start + n].to(torch.float32))
+        start += n
+    return out.to(torch.bfloat16)
+
+
+def dispatch_bytes(plan: DispatchPlan, rank: int, hidden_size: int, topk: int) -> int:
+    """Bytes this rank puts on the wire for one layer (dispatch rows + ids + weights, and the combine rows it will
+    get back are the same count): rows to other ranks only."""
+    remote = sum(c for r, c in enumerate(plan.send_counts) if r != rank)
+    return remote * (hidden_size * 2 + topk * 8) + remote * hidden_size * 2
