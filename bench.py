@@ -1,17 +1,25 @@
 #!/usr/bin/env python
-"""Benchmark of the MXFP8 dense hot path (quantize + block-scaled GEMM) on B200.
+"""Benchmarks of the MXFP8 dense / MoE hot path on B200. Prints ONE JSON line on rank 0.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload dense|moe]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-One step = one pass of ``fso.dense.linear`` (1x32 activation quantizer, then the tcgen05 GEMM) over one synthetic
-batch of the Llama-3-8B gate_up projection (M=8192, N=28672, K=4096; operands larger than L2, so every timed step
-streams them from HBM). With N > 1 (launched by torch.distributed.run, one rank per GPU) the weight rows are split
-N-ways (column parallel, no data-path collective) and ``value`` is the whole job's 2*M*N*K over the slowest
-rank's device time. Prints ONE JSON line on rank 0.
+Workloads (``--workload``):
 
-``--impl reference`` times the reference's CPU statement of the same path (the fp32 dequantize-then-matmul oracle
-under ``oracle/``, the only thing that runs there) on this box's host cores, on a bounded row sample of the same
-workload, and prints the same line with ``"impl": "reference"``.
+  dense     (default) the headline: one step = one pass of ``fso.dense.linear`` (1x32 activation quantizer, then the
+            tcgen05 block-scaled GEMM) over the Llama-3-8B gate_up projection, M=8192, N=28672, K=4096. Operands and
+            output exceed L2, so every step streams them from HBM. With N > 1 (torch.distributed.run, one rank per
+            GPU) the weight rows are split N ways (column parallel, no data-path collective); ``value`` is the whole
+            job's 2*M*N*K over the slowest rank's device time.
+  moe       one DeepSeek-V3-shaped MoE layer (256 experts, top-8, H=7168, I=2048), 4096 tokens per GPU, experts
+            sharded 256/N per GPU with NCCL all-to-all-v dispatch and combine (weak scaling); ``--moe-config mixtral``
+            runs the 8-expert top-2 H=4096 I=14336 layer on one GPU. Metric: tokens/s.
+  decode    dense linears at M=16 over the four Llama-3-8B shapes, CUDA-graph replay over rotated weight copies
+            (cold weights). Metric: achieved weight-stream GB/s (worst of the four shapes).
+  quantize  the activation quantizer alone on [8192, 4096]. Metric: GB/s.
+
+``--impl reference`` times the reference's CPU statement of the same workload (the fp32 dequantize-then-matmul
+oracle under ``oracle/``, the only thing that runs there) on this box's host cores, on a bounded sample, and prints
+the same line with ``"impl": "reference"``.
 """
 import argparse
 import json
@@ -23,13 +31,13 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-M, N, K = 8192, 28672, 4096
-WORKLOAD = "llama3-8b gate_up linear: x bf16 [8192, 4096] ~ N(0,1), w bf16 [28672, 4096] ~ N(0,0.02) as MXFP8"
-METRIC = "mxfp8_gemm_tflops"
-UNIT = "TFLOP/s"
+LLAMA = {"qkv": (6144, 4096), "gate_up": (28672, 4096), "o_proj": (4096, 4096), "down": (4096, 14336)}
+MOE_CONFIGS = {"dsv3": dict(E=256, k=8, H=7168, I=2048, T=4096, renorm=False),
+               "mixtral": dict(E=8, k=2, H=4096, I=14336, T=8192, renorm=True)}
+L2_BYTES = 126e6
 
 
-def _peaks():
+def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
@@ -68,7 +76,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:  # noqa: BLE001
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.005)
 
     def __enter__(self):
         if self._nv is not None:
@@ -89,22 +97,98 @@ class ClockSampler:
                 "samples": len(s)}
 
 
-def _inputs(torch, rows_n: int, seed: int):
+class Dist:
+    """The process group of this run (one rank per GPU under torch.distributed.run, or a single process)."""
+
+    def __init__(self, torch):
+        import torch.distributed as dist
+
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (B200); this arm has no CPU path")
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(values, dtype=self.torch.float64, device="cuda")
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def close(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed_steps(torch, d: Dist, step, steps: int, warmup: int, per_step_events: bool = False):
+    """W untimed steps, then exactly K steps between barrier + synchronize on both sides, timed with CUDA events on
+    the launching stream. Returns (total ms, clocks summary, [per-step event pairs])."""
+    stream = torch.cuda.current_stream()
+    for _ in range(warmup):
+        step(None)
+    d.barrier()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)] \
+        if per_step_events else None
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(d.local) as clocks:
+        d.barrier()
+        t0.record(stream)
+        for i in range(steps):
+            step(pairs[i] if pairs else None)
+        t1.record(stream)
+        d.barrier()
+    return t0.elapsed_time(t1), clocks.summary(), pairs
+
+
+def base_line(args, d, metric, unit, value, ms_step, scaling, dtype, config):
+    return {"metric": metric, "value": value, "unit": unit, "n_gpus": d.world if d else args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": config}
+
+
+# ====================================================================================================== dense
+
+DENSE_M, DENSE_N, DENSE_K = 8192, 28672, 4096
+
+
+def dense_shape(args):
+    if args.shape:
+        return tuple(int(v) for v in args.shape.split(","))
+    return DENSE_M, DENSE_N, DENSE_K
+
+
+def dense_workload_name(m, n, k):
+    if (m, n, k) == (DENSE_M, DENSE_N, DENSE_K):
+        return f"llama3-8b gate_up linear: x bf16 [{m}, {k}] ~ N(0,1), w bf16 [{n}, {k}] ~ N(0,0.02) as MXFP8"
+    return f"dense linear override: x bf16 [{m}, {k}], w bf16 [{n}, {k}] as MXFP8"
+
+
+def dense_inputs(torch, m, n, k, seed=0):
     g = torch.Generator(device="cpu").manual_seed(seed)
-    x = torch.randn(M, K, generator=g, dtype=torch.float32).to(torch.bfloat16)
-    w = (0.02 * torch.randn(rows_n, K, generator=g, dtype=torch.float32)).to(torch.bfloat16)
+    x = torch.randn(m, k, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g, dtype=torch.float32)).to(torch.bfloat16)
     return x, w
 
 
-def cpu_reference_tflops(torch, budget_s: float, threads: int):
+def dense_cpu_runner(torch, m, n, k, budget_s: float, threads: int):
     """The oracle's dense path on host cores: quantize the activation rows (1x32 rule), dequantize, fp32 matmul
-    against the dequantized MXFP8 weight. Timed on a row sample sized to about ``budget_s`` seconds."""
+    against the dequantized MXFP8 weight. Returns (run(rows) -> (seconds, y), rows sized to about budget_s)."""
     from oracle import oracle as O
 
     O.build()
     torch.set_num_threads(threads)
-    x, w = _inputs(torch, N, 0)
-    wq, ws = O.quantize_1x32(w[:N])
+    x, w = dense_inputs(torch, m, n, k)
+    wq, ws = O.quantize_1x32(w)
     wd = torch.from_numpy(O.dequant(wq, ws))
 
     def run(rows):
@@ -112,87 +196,57 @@ def cpu_reference_tflops(torch, budget_s: float, threads: int):
         xq, xs = O.quantize_1x32(x[:rows])
         xd = torch.from_numpy(O.dequant(xq, xs))
         y = (xd @ wd.t()).to(torch.bfloat16)
-        dt = time.perf_counter() - t0
-        return dt, y
+        return time.perf_counter() - t0, y
 
-    dt_probe, _ = run(32)
-    rows = int(max(32, min(M, 32 * budget_s / max(dt_probe, 1e-6))))
-    rows = max(32, rows // 32 * 32)
+    probe = min(32, m)
+    dt_probe, _ = run(probe)
+    rows = int(max(probe, min(m, probe * budget_s / max(dt_probe, 1e-6))))
+    rows = max(probe, rows // 32 * 32) if rows >= 32 else rows
     return run, rows
 
 
-def reference_arm(args):
+def dense_reference(args):
     import torch
 
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return 0
+    if int(os.environ.get("RANK", "0")) != 0:
+        return None
+    m, n, k = dense_shape(args)
     threads = os.cpu_count() or 1
-    budget = 60.0 / max(1, args.steps + args.warmup)
-    run, rows = cpu_reference_tflops(torch, min(10.0, max(1.0, budget)), threads)
+    budget = min(10.0, max(1.0, 60.0 / max(1, args.steps + args.warmup)))
+    run, rows = dense_cpu_runner(torch, m, n, k, budget, threads)
     for _ in range(args.warmup):
         run(rows)
-    times = []
-    for _ in range(args.steps):
-        times.append(run(rows)[0])
-    dt = sum(times) / len(times)
-    val = 2.0 * rows * N * K / dt / 1e12
-    sample = f"first {rows} of {M} activation rows against the full [{N}, {K}] weight per step"
-    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K, "sample": sample},
-            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
-            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
-    print(json.dumps(line))
-    return 0
+    dt = sum(run(rows)[0] for _ in range(args.steps)) / args.steps
+    val = 2.0 * rows * n * k / dt / 1e12
+    sample = f"first {rows} of {m} activation rows against the full [{n}, {k}] weight per step"
+    line = base_line(args, None, "mxfp8_gemm_tflops", "TFLOP/s", val, dt * 1e3, "strong", "f32",
+                     {"workload": dense_workload_name(m, n, k), "M": m, "N": n, "K": k, "sample": sample})
+    line.update({"impl": "reference",
+                 "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+                 "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                 "gpu_launches": 0})
+    return line
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shape", default=None, help="M,N,K override (profiling captures on a smaller case)")
-    args = ap.parse_args()
-    if args.shape:
-        global M, N, K, WORKLOAD
-        M, N, K = (int(v) for v in args.shape.split(","))
-        WORKLOAD = f"dense linear override: x bf16 [{M}, {K}], w bf16 [{N}, {K}] as MXFP8"
-    args.warmup = max(3, args.warmup) if args.impl == "ours" else max(0, args.warmup)
-    if args.impl == "reference":
-        return reference_arm(args)
-
+def dense_ours(args):
     import torch
-    import torch.distributed as dist
 
     import fish_scales_ops_b200 as fso
+    from fish_scales_ops_b200 import _ops, parallel
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for this arm")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    assert N % (128 * world) == 0
-    n_local = N // world
+    d = Dist(torch)
+    m, n, k = dense_shape(args)
+    r0, r1 = parallel.column_shard(n, d.world, d.rank)
+    n_local = r1 - r0
     fso.build()
-
-    x_cpu, w_cpu = _inputs(torch, N, 0)
-    w_local = w_cpu[rank * n_local:(rank + 1) * n_local].cuda()
-    weight = fso.dense.prepare_weight(w_local, format="mxfp8")
-    del w_local
+    x_cpu, w_cpu = dense_inputs(torch, m, n, k)
+    weight = fso.dense.prepare_weight(w_cpu[r0:r1].cuda(), format="mxfp8")
     x = x_cpu.cuda()
     x_host = x_cpu.pin_memory()
-    y_host = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+    y_host = torch.empty((m, n_local), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.current_stream()
 
-    def step(ev=None):
+    def step(ev):
         xq, sx = fso.dense.quantize_activation(x)
         if ev is not None:
             ev[0].record(stream)
@@ -201,91 +255,345 @@ def main():
             ev[1].record(stream)
         return y
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    ms_total, clocks, pairs = timed_steps(torch, d, step, args.steps, args.warmup, per_step_events=True)
+    gemm_ms = sum(a.elapsed_time(b) for a, b in pairs) / args.steps
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    gemm_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        barrier()
-        t0.record(stream)
-        for i in range(args.steps):
-            step(gemm_ev[i])
-        t1.record(stream)
-        barrier()
-    ms_total = t0.elapsed_time(t1)
-    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_ev) / args.steps
-
-    # end to end through the public call with host buffers: H2D of the step's activation, linear, D2H of its result
-    def e2e_step():
+    # end to end through the public call with host buffers: H2D of the activation, linear, D2H of the result
+    def e2e_step(_):
         xd = x_host.to("cuda", non_blocking=True)
-        y = fso.dense.linear(xd, weight)
-        y_host.copy_(y, non_blocking=True)
+        y_host.copy_(fso.dense.linear(xd, weight), non_blocking=True)
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
     e_steps = max(3, min(args.steps, 20))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(e_steps):
-        e2e_step()
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms, _, _ = timed_steps(torch, d, e2e_step, e_steps, 2)
+    ms_total, e2e_ms, gemm_ms = d.max_over_ranks([ms_total, e2e_ms, gemm_ms])
+    status = _ops.device_status()
+    if d.rank != 0:
+        d.close()
+        return None
 
-    times = torch.tensor([ms_total, e2e_ms, gemm_ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, gemm_ms = (float(v) for v in times.tolist())
+    flops = 2.0 * m * n * k
+    ms_step = ms_total / args.steps
+    pk = peaks()
+    fp8_peak = 2.0 * pk["bf16_burst"]
+    gemm_tflops = 2.0 * m * n_local * k / (gemm_ms * 1e-3) / 1e12
+    line = base_line(args, d, "mxfp8_gemm_tflops", "TFLOP/s", flops / (ms_step * 1e-3) / 1e12, ms_step, "strong",
+                     "fp8_e4m3",
+                     {"workload": dense_workload_name(m, n, k), "M": m, "N": n, "K": k,
+                      "parallelism": f"column-parallel N-split x{d.world} (no collective)",
+                      "step": "quantize_activation + linear(xq, x_scale) == linear(x): 2 kernels",
+                      "l2": "operands and output of a step exceed the 126 MB L2 (x 64 MB, w 117 MB, y 470 MB at N=1)"})
+    line["roofline"] = {
+        "bound": "tensor", "kernel": "gemm_mxf8_kernel<256, bf16>", "achieved": gemm_tflops, "peak": fp8_peak,
+        "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
+        "peak_source": f"2 x {pk['source']} bf16 burst ({pk['bf16_burst']} TF/s): an fp8 MMA does twice the bf16 "
+                       f"work per cycle; nominal dense fp8 is 4500",
+        "frac_of_nominal": gemm_tflops / 4500.0, "flops_per_launch": 2.0 * m * n_local * k, "ms_per_launch": gemm_ms}
+    line["e2e"] = {"value": flops / (e2e_ms / e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                   "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n_local * 2,
+                   "ms_per_step": e2e_ms / e_steps}
+    line["gpu_launches"] = 2 * args.steps
+    line["clocks"] = clocks
+    line["device_status"] = status
+    if not args.no_cpu_baseline and d.world == 1:
+        threads = os.cpu_count() or 1
+        run, rows = dense_cpu_runner(torch, m, n, k, 10.0, threads)
+        dt, y_cpu = run(rows)
+        y_gpu = step(None)[:rows].float().cpu()
+        line["cpu_baseline"] = {
+            "value": 2.0 * rows * n * k / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"first {rows} of {m} activation rows against the full weight, one pass",
+            "rel_frobenius_gpu_vs_cpu": float((y_gpu - y_cpu.float()).norm() / y_cpu.float().norm())}
+    d.close()
+    return line
+
+
+# ====================================================================================================== MoE
+
+def moe_inputs(torch, cfg, tokens, seed, device="cpu"):
+    """hidden ~ N(0,1), router logits ~ N(0,1) -> softmax top-k (renormalised for the Mixtral config)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    hidden = torch.randn(tokens, cfg["H"], generator=g, dtype=torch.float32).to(torch.bfloat16)
+    p = torch.softmax(torch.randn(tokens, cfg["E"], generator=g, dtype=torch.float32), dim=-1)
+    w, ids = torch.topk(p, cfg["k"], dim=-1)
+    if cfg["renorm"]:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return hidden.to(device), ids.to(torch.int32).to(device), w.to(device)
+
+
+def moe_expert_weights(torch, cfg, e0, e1, device):
+    """bf16 ~ N(0, 0.02) experts [e0, e1), generated expert by expert on the device (seeded per expert, so every
+    rank and the CPU arm see the same expert e whatever the sharding)."""
+    n = e1 - e0
+    w13 = torch.empty((n, 2 * cfg["I"], cfg["H"]), dtype=torch.bfloat16, device=device)
+    w2 = torch.empty((n, cfg["H"], cfg["I"]), dtype=torch.bfloat16, device=device)
+    for j, e in enumerate(range(e0, e1)):
+        g = torch.Generator(device=device).manual_seed(1000 + e)
+        w13[j] = (0.02 * torch.randn(2 * cfg["I"], cfg["H"], generator=g, device=device)).to(torch.bfloat16)
+        w2[j] = (0.02 * torch.randn(cfg["H"], cfg["I"], generator=g, device=device)).to(torch.bfloat16)
+    return w13, w2
+
+
+def moe_cpu_runner(torch, cfg, sample_tokens, threads):
+    """The oracle's MoE layer on host cores for a token sample, with only the experts that sample touches
+    materialised (quantized weights prepared once, outside the timed call; the call dequantizes them, runs the fp32
+    matmuls and requantizes the SwiGLU intermediate). Returns (run() -> (seconds, out), inputs)."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    O.build()
+    torch.set_num_threads(threads)
+    hidden, ids, w = moe_inputs(torch, cfg, sample_tokens, 7)
+    used = sorted(set(ids.reshape(-1).tolist()))
+    remap = {e: j for j, e in enumerate(used)}
+    ids_l = torch.tensor([[remap[int(v)] for v in row] for row in ids.tolist()], dtype=torch.int32)
+    q13, s13, q2, s2 = [], [], [], []
+    for e in used:
+        w13, w2 = moe_expert_weights(torch, cfg, e, e + 1, "cpu")
+        a, b = O.quantize_1x32(w13[0], interleave_i=cfg["I"])
+        c, dd = O.quantize_1x32(w2[0])
+        q13.append(a), s13.append(b), q2.append(c), s2.append(dd)
+    q13, s13, q2, s2 = np.stack(q13), np.stack(s13), np.stack(q2), np.stack(s2)
+
+    def run():
+        t0 = time.perf_counter()
+        out = O.moe_layer(hidden, q13, s13, q2, s2, ids_l, w, interleaved=True)
+        return time.perf_counter() - t0, out
+
+    return run, (hidden, ids, w)
+
+
+MOE_CPU_SAMPLE = {"dsv3": 4, "mixtral": 64}
+
+
+def moe_reference(args):
+    import torch
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return None
+    cfg = MOE_CONFIGS[args.moe_config]
+    threads = os.cpu_count() or 1
+    sample = MOE_CPU_SAMPLE[args.moe_config]
+    run, _ = moe_cpu_runner(torch, cfg, sample, threads)
+    for _ in range(min(args.warmup, 1)):
+        run()
+    n = max(1, min(args.steps, 5))
+    dt = sum(run()[0] for _ in range(n)) / n
+    v = sample / dt
+    note = f"{sample} tokens with their real routing; only the experts they touch are prepared (outside the timed call)"
+    line = base_line(args, None, "moe_layer_tokens_per_s", "tokens/s", v, dt * 1e3, "weak", "f32",
+                     {"workload": f"{args.moe_config} MoE layer", **{k_: cfg[k_] for k_ in ("E", "k", "H", "I")},
+                      "sample": note})
+    line.update({"impl": "reference",
+                 "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": note},
+                 "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                 "gpu_launches": 0})
+    return line
+
+
+def moe_ours(args):
+    import torch
+
+    import fish_scales_ops_b200 as fso
+    from fish_scales_ops_b200 import _ops, parallel
+
+    d = Dist(torch)
+    cfg = MOE_CONFIGS[args.moe_config]
+    if d.world > 1 and args.moe_config != "dsv3":
+        raise SystemExit("the multi-GPU MoE workload is the DeepSeek-V3 config (expert parallel)")
+    fso.build()
+    e0, e1 = parallel.expert_shard(cfg["E"], d.world, d.rank)
+    w13, w2 = moe_expert_weights(torch, cfg, e0, e1, "cuda")
+    experts = fso.moe.prepare_experts(w13, w2, format="mxfp8")
+    del w13, w2
+    torch.cuda.empty_cache()
+    tokens = cfg["T"]
+    hidden_cpu, ids_cpu, w_cpu = moe_inputs(torch, cfg, tokens, 100 + d.rank)
+    hidden, ids, wts = hidden_cpu.cuda(), ids_cpu.cuda(), w_cpu.cuda()
+    hidden_host = hidden_cpu.pin_memory()
+    out_host = torch.empty((tokens, cfg["H"]), dtype=torch.bfloat16).pin_memory()
+
+    def run(h):
+        if d.world == 1:
+            return fso.moe.layer(h, experts, ids, wts)
+        return parallel.expert_parallel_layer(h, experts, ids, wts, num_experts_global=cfg["E"])
+
+    ms_total, clocks, _ = timed_steps(torch, d, lambda _: run(hidden), args.steps, args.warmup)
+
+    def e2e_step(_):
+        out_host.copy_(run(hidden_host.to("cuda", non_blocking=True)), non_blocking=True)
+
+    e_steps = max(3, min(args.steps, 10))
+    e2e_ms, _, _ = timed_steps(torch, d, e2e_step, e_steps, 2)
+    ms_total, e2e_ms = d.max_over_ranks([ms_total, e2e_ms])
+    status = _ops.device_status()
+    if d.rank != 0:
+        d.close()
+        return None
+    ms_step = ms_total / args.steps
+    total_tokens = tokens * d.world
+    pairs = total_tokens * cfg["k"]
+    flops = 6.0 * pairs * cfg["H"] * cfg["I"]
+    pk = peaks()
+    fp8_peak = 2.0 * pk["bf16_burst"]
+    weight_bytes = (e1 - e0) * 3 * cfg["H"] * cfg["I"] * (1 + 1 / 32)
+    t_mem = weight_bytes / (pk["hbm_gbs"] * 1e9)
+    t_cmp = flops / d.world / (fp8_peak * 1e12)
+    line = base_line(args, d, "moe_layer_tokens_per_s", "tokens/s", total_tokens / (ms_step * 1e-3), ms_step, "weak",
+                     "fp8_e4m3",
+                     {"workload": f"{args.moe_config} MoE layer, {tokens} tokens per GPU, uniform softmax top-k routing",
+                      **{k_: cfg[k_] for k_ in ("E", "k", "H", "I")},
+                      "parallelism": f"expert parallel x{d.world} (all-to-all-v dispatch + combine)" if d.world > 1
+                      else "single GPU", "l2": "expert weights of a step exceed L2"})
+    line["roofline"] = {
+        "bound": "hbm" if t_mem > t_cmp else "tensor", "kernel": "whole layer (route, gather, FC1, FC2, combine)",
+        "achieved": flops / d.world / (ms_step * 1e-3) / 1e12, "peak": fp8_peak, "unit": "TFLOP/s",
+        "frac": max(t_mem, t_cmp) / (ms_step * 1e-3), "traffic": None,
+        "note": f"frac = max(weight bytes / measured HBM, 6*P*H*I / (2 x bf16 burst)) / step time per GPU; "
+                f"weight stream {t_mem * 1e3:.3f} ms, tensor {t_cmp * 1e3:.3f} ms"}
+    line["e2e"] = {"value": total_tokens / (e2e_ms / e_steps * 1e-3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": tokens * cfg["H"] * 2, "d2h_bytes_per_step": tokens * cfg["H"] * 2,
+                   "ms_per_step": e2e_ms / e_steps}
+    line["gpu_launches"] = (7 if tokens * cfg["k"] > 1024 else 5) * args.steps
+    line["clocks"] = clocks
+    line["device_status"] = status
+    if not args.no_cpu_baseline and d.world == 1:
+        threads = os.cpu_count() or 1
+        sample = MOE_CPU_SAMPLE[args.moe_config]
+        cpu_run, (h_s, ids_s, w_s) = moe_cpu_runner(torch, cfg, sample, threads)
+        dt, out_cpu = cpu_run()
+        v = sample / dt
+        out_gpu = fso.moe.layer(h_s.cuda(), experts, ids_s.cuda(), w_s.cuda()).float().cpu()
+        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": f"{sample} tokens with their real routing ({dt:.2f} s)",
+                                "rel_frobenius_gpu_vs_cpu": float((out_gpu - out_cpu).norm() / out_cpu.norm())}
+    d.close()
+    return line
+
+
+# ====================================================================================================== decode / quantize
+
+def graph_replay_us(torch, make_call, reps: int, iters: int):
+    """Median device time per call of ``reps`` calls captured into one CUDA graph and replayed ``iters`` times."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(reps):
+            make_call(i)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(reps):
+                make_call(i)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(5):
+        e0.record()
+        for _ in range(iters):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / iters / reps * 1e3)
+    return sorted(times)[len(times) // 2]
+
+
+def decode_ours(args):
+    import torch
+
+    import fish_scales_ops_b200 as fso
     from fish_scales_ops_b200 import _ops
 
-    status = _ops.device_status()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank != 0:
-        return 0
+    d = Dist(torch)
+    fso.build()
+    m = args.decode_m
+    pk = peaks()
+    cells = {}
+    with ClockSampler(d.local) as clocks:
+        for name, (n, k) in LLAMA.items():
+            wbytes = n * k * (1 + 1 / 32)
+            copies = int(2 * L2_BYTES / wbytes) + 1          # rotated copies: copies * bytes >= 2 x L2 (cold weights)
+            weights = [fso.dense.prepare_weight(dense_inputs(torch, 1, n, k, seed=10 + c)[1].cuda(), format="mxfp8")
+                       for c in range(copies)]
+            x = dense_inputs(torch, m, n, k, seed=3)[0].cuda()
+            xq, sx = fso.dense.quantize_activation(x)
+            us_gemm = graph_replay_us(torch, lambda i: fso.dense.linear(xq, weights[i % copies], x_scale=sx), copies,
+                                      max(5, args.steps // 5))
+            us_lin = graph_replay_us(torch, lambda i: fso.dense.linear(x, weights[i % copies]), copies,
+                                     max(5, args.steps // 5))
+            nbytes = wbytes + m * k * (1 + 1 / 32) + 2 * m * n
+            cells[name] = {"N": n, "K": k, "gemm_us": us_gemm, "linear_us": us_lin, "gemm_gbs": nbytes / us_gemm / 1e3,
+                           "frac_of_measured_hbm": nbytes / us_gemm / 1e3 / pk["hbm_gbs"], "weight_copies": copies}
+            del weights
+    worst = min(cells.values(), key=lambda c: c["gemm_gbs"])
+    total_us = sum(c["linear_us"] for c in cells.values())
+    line = base_line(args, d, "dense_decode_weight_stream_gbs", "GB/s", worst["gemm_gbs"], total_us / 1e3, "strong",
+                     "fp8_e4m3", {"workload": f"llama3-8b dense linears at M={m}, CUDA-graph replay, cold weights",
+                                  "cells": cells, "l2": "rotated weight copies of at least 2 x L2 per shape"})
+    line["roofline"] = {"bound": "hbm", "kernel": "gemm_mxf8_kernel<16, swapped> (+ split-K reduce)",
+                        "achieved": worst["gemm_gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                        "frac": worst["gemm_gbs"] / pk["hbm_gbs"], "traffic": None,
+                        "peak_source": f"{pk['source']} copy bandwidth"}
+    line["gpu_launches"] = None
+    line["clocks"] = clocks.summary()
+    line["device_status"] = _ops.device_status()
+    d.close()
+    return line
 
-    flops = 2.0 * M * N * K
-    ms_step = ms_total / args.steps
-    value = flops / (ms_step * 1e-3) / 1e12
-    peaks = _peaks()
-    fp8_peak = 2.0 * peaks["bf16_burst"]
-    gemm_tflops = 2.0 * M * n_local * K / (gemm_ms * 1e-3) / 1e12
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K, "parallelism": f"column-parallel N-split x{world}",
-                   "step": "quantize_activation + linear(xq, x_scale) == linear(x) (2 kernels)",
-                   "l2": "operands (64 MB + 117 MB) and output (470 MB) exceed the 126 MB L2"},
-        "roofline": {"bound": "tensor", "kernel": "gemm_mxf8_kernel<256>", "achieved": gemm_tflops, "peak": fp8_peak,
-                     "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
-                     "peak_source": f"2 x {peaks['source']} bf16 burst ({peaks['bf16_burst']} TF/s); nominal fp8 4500",
-                     "frac_of_nominal": gemm_tflops / 4500.0, "flops_per_launch": 2.0 * M * n_local * K,
-                     "ms_per_launch": gemm_ms},
-        "e2e": {"value": flops / (e2e_ms / e_steps * 1e-3) / 1e12, "unit": UNIT,
-                "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * n_local * 2, "ms_per_step": e2e_ms / e_steps},
-        "gpu_launches": 2 * args.steps,
-        "clocks": clocks.summary(),
-        "device_status": status,
-    }
-    if not args.no_cpu_baseline and world == 1:
-        threads = os.cpu_count() or 1
-        run, rows = cpu_reference_tflops(torch, 10.0, threads)
-        dt, y_cpu = run(rows)
-        y_gpu = step()[:rows].float().cpu()
-        err = float((y_gpu - y_cpu.float()).norm() / y_cpu.float().norm())
-        line["cpu_baseline"] = {"value": 2.0 * rows * N * K / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"first {rows} of {M} activation rows against the full weight, one pass",
-                                "rel_frobenius_gpu_vs_cpu": err}
-    print(json.dumps(line))
+
+def quantize_ours(args):
+    import torch
+
+    import fish_scales_ops_b200 as fso
+    from fish_scales_ops_b200 import _ops
+
+    d = Dist(torch)
+    fso.build()
+    m, k = 8192, 4096
+    x = dense_inputs(torch, m, 128, k)[0].cuda()
+    copies = 4
+    xs = [x.clone() for _ in range(copies)]
+    ms_total, clocks, _ = timed_steps(torch, d, lambda _: [fso.dense.quantize_activation(v) for v in xs], args.steps,
+                                      args.warmup)
+    us = ms_total / args.steps / copies * 1e3
+    nbytes = m * k * (3 + 1 / 32)
+    pk = peaks()
+    line = base_line(args, d, "quantize_1x32_gbs", "GB/s", nbytes / us / 1e3, us / 1e3, "strong", "bf16->fp8_e4m3",
+                     {"workload": f"1x32 MXFP8 activation quantizer on bf16 [{m}, {k}], {copies} rotated inputs",
+                      "l2": "4 x 64 MB inputs + outputs exceed L2"})
+    line["roofline"] = {"bound": "hbm", "kernel": "quantize_1x32_kernel", "achieved": nbytes / us / 1e3,
+                        "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": nbytes / us / 1e3 / pk["hbm_gbs"],
+                        "traffic": None, "peak_source": f"{pk['source']} copy bandwidth"}
+    line["gpu_launches"] = copies * args.steps
+    line["clocks"] = clocks
+    line["device_status"] = _ops.device_status()
+    d.close()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize"])
+    ap.add_argument("--moe-config", default="dsv3", choices=sorted(MOE_CONFIGS))
+    ap.add_argument("--decode-m", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shape", default=None, help="dense workload: M,N,K override (profiling on a smaller case)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.warmup = max(0, args.warmup)
+        line = moe_reference(args) if args.workload == "moe" else dense_reference(args)
+    else:
+        args.warmup = max(3, args.warmup)
+        line = {"dense": dense_ours, "moe": moe_ours, "decode": decode_ours, "quantize": quantize_ours}[args.workload](
+            args)
+    if line is not None:
+        print(json.dumps(line))
     return 0
 
 
