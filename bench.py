@@ -407,7 +407,7 @@ def moe_ours(args):
     experts = fso.moe.prepare_experts(w13, w2, format="mxfp8")
     del w13, w2
     torch.cuda.empty_cache()
-    tokens = cfg["T"]
+    tokens = args.moe_tokens or cfg["T"]
     hidden_cpu, ids_cpu, w_cpu = moe_inputs(torch, cfg, tokens, 100 + d.rank)
     hidden, ids, wts = hidden_cpu.cuda(), ids_cpu.cuda(), w_cpu.cuda()
     hidden_host = hidden_cpu.pin_memory()
@@ -581,6 +581,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize"])
     ap.add_argument("--moe-config", default="dsv3", choices=sorted(MOE_CONFIGS))
+    ap.add_argument("--moe-tokens", type=int, default=0, help="moe workload: tokens per GPU override")
     ap.add_argument("--decode-m", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--shape", default=None, help="dense workload: M,N,K override (profiling on a smaller case)")

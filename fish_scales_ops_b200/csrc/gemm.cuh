@@ -47,11 +47,13 @@ struct GemmParams {
     int64_t out_rows;          // rows of the output (row stride of one split's partial = out_rows * ldo)
 };
 
-template <int BN>
+template <int BN, int EPI = 0>
 struct GemmCfg {
     static constexpr int kBM = 128;
     static constexpr int kBK = 128;                                   // bytes == elements along K per stage
-    static constexpr int kEpiWarps = BN >= 128 ? 8 : 4;
+    // epilogue warps: 4 quarters x {1, 2, 4} column slices. The SwiGLU epilogue takes 64-column slices so that a
+    // slice fits in registers and the accumulator can be handed back before the activation math starts.
+    static constexpr int kEpiWarps = EPI == 2 /* EPI_SWIGLU */ ? 16 : BN >= 128 ? 8 : 4;
     static constexpr int kThreads = 128 + 32 * kEpiWarps;
     static constexpr int kAccStages = BN == 256 ? 1 : 2;
     static constexpr int kABytes = kBM * kBK;
@@ -134,11 +136,11 @@ __device__ __forceinline__ float silu_mul(float g, float u)
 }
 
 template <int BN, int EPI, bool kSwap, bool kGrouped>
-__global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<BN, EPI>::kThreads, 1)
 gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
     const GemmParams p)
 {
-    using C = GemmCfg<BN>;
+    using C = GemmCfg<BN, EPI>;
     constexpr int S = C::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint32_t const raw = smem_u32(smem_raw);
@@ -308,49 +310,49 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             bool released = false;
 
             if constexpr (EPI == EPI_SWIGLU) {
-                // interleaved (gate, up) columns -> 64 outputs per warp = two 1x32 blocks per row
+                // 64 interleaved (gate, up) accumulator columns per warp -> 32 outputs = one 1x32 block per row.
+                // The slice is drained into registers and the accumulator handed back before the math starts.
+                static_assert(kColsPerWarp == 64, "one 1x32 output block per warp");
                 int const inter = p.ldo;
-                uint8_t* const drow = static_cast<uint8_t*>(p.out) + static_cast<int64_t>(a_row) * inter
-                    + c.b_tile * (BN / 2) + half * (kColsPerWarp / 2);
-                uint32_t bytes2 = 0;
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(t_row + half * 64, r0);
+                tmem_ld_32x32(t_row + half * 64 + 32, r1);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                released = true;
+                float h[32];
+                float amax = 0.f;
 #pragma unroll
-                for (int blk = 0; blk < kColsPerWarp / 64; ++blk) {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld_32x32(t_row + half * kColsPerWarp + blk * 64, r0);
-                    tmem_ld_32x32(t_row + half * kColsPerWarp + blk * 64 + 32, r1);
-                    tmem_ld_wait();
-                    float h[32];
-                    float amax = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        h[j] = silu_mul(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-                        h[16 + j] = silu_mul(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-                        amax = fmaxf(amax, fmaxf(fabsf(h[j]), fabsf(h[16 + j])));
-                    }
-                    amax = fmaxf(amax, 1e-10f);
-                    float qs;
-                    uint32_t const byte = e8m0_from_amax(amax, qs);
-                    bytes2 |= byte << (8 * blk);
-                    uint4 o0, o1;
-                    o0.x = fp8x4(__fmul_rn(h[0], qs), __fmul_rn(h[1], qs), __fmul_rn(h[2], qs), __fmul_rn(h[3], qs));
-                    o0.y = fp8x4(__fmul_rn(h[4], qs), __fmul_rn(h[5], qs), __fmul_rn(h[6], qs), __fmul_rn(h[7], qs));
-                    o0.z = fp8x4(__fmul_rn(h[8], qs), __fmul_rn(h[9], qs), __fmul_rn(h[10], qs), __fmul_rn(h[11], qs));
-                    o0.w = fp8x4(__fmul_rn(h[12], qs), __fmul_rn(h[13], qs), __fmul_rn(h[14], qs), __fmul_rn(h[15], qs));
-                    o1.x = fp8x4(__fmul_rn(h[16], qs), __fmul_rn(h[17], qs), __fmul_rn(h[18], qs), __fmul_rn(h[19], qs));
-                    o1.y = fp8x4(__fmul_rn(h[20], qs), __fmul_rn(h[21], qs), __fmul_rn(h[22], qs), __fmul_rn(h[23], qs));
-                    o1.z = fp8x4(__fmul_rn(h[24], qs), __fmul_rn(h[25], qs), __fmul_rn(h[26], qs), __fmul_rn(h[27], qs));
-                    o1.w = fp8x4(__fmul_rn(h[28], qs), __fmul_rn(h[29], qs), __fmul_rn(h[30], qs), __fmul_rn(h[31], qs));
-                    if (a_row < p.out_rows) {
-                        uint4* dst = reinterpret_cast<uint4*>(drow + blk * 32);
-                        dst[0] = o0;
-                        dst[1] = o1;
-                    }
+                for (int j = 0; j < 16; ++j) {
+                    h[j] = silu_mul(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                    h[16 + j] = silu_mul(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                    amax = fmaxf(amax, fmaxf(fabsf(h[j]), fabsf(h[16 + j])));
                 }
+                amax = fmaxf(amax, 1e-10f);
+                float qs;
+                uint32_t const byte = e8m0_from_amax(amax, qs);
+                uint32_t o[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    o[v] = fp8x4(__fmul_rn(h[4 * v], qs), __fmul_rn(h[4 * v + 1], qs), __fmul_rn(h[4 * v + 2], qs),
+                        __fmul_rn(h[4 * v + 3], qs));
                 if (a_row < p.out_rows) {
-                    // this warp owns bytes [2*half, 2*half+2) of the row's scale word for K block b_tile of the output
-                    uint8_t* const w = reinterpret_cast<uint8_t*>(p.out_sf)
-                        + sf_word_index(a_row, c.b_tile, inter / 128) * 4 + half * 2;
-                    *reinterpret_cast<uint16_t*>(w) = static_cast<uint16_t>(bytes2);
+                    uint8_t* const dst = static_cast<uint8_t*>(p.out) + static_cast<int64_t>(a_row) * inter
+                        + c.b_tile * (BN / 2) + half * 32;
+                    if (p.out_align32) {
+                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                     ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]),
+                                     "r"(o[6]), "r"(o[7])
+                                     : "memory");
+                    } else {
+                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    // byte `half` (0..3) of the row's scale word for K block b_tile of the output
+                    reinterpret_cast<uint8_t*>(p.out_sf)[sf_word_index(a_row, c.b_tile, inter / 128) * 4 + half]
+                        = static_cast<uint8_t>(byte);
                 }
             } else if constexpr (!kSwap && EPI == EPI_BF16) {
                 // row = output row, columns = output columns. The accumulator slice is drained into packed bf16

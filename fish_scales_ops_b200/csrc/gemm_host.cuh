@@ -128,7 +128,7 @@ template <int BN, int EPI, bool kSwap, bool kGrouped>
 inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int grid,
     cudaStream_t stream)
 {
-    using C = GemmCfg<BN>;
+    using C = GemmCfg<BN, EPI>;
     static std::atomic<uint64_t> done{0};
     auto kernel = gemm_mxf8_kernel<BN, EPI, kSwap, kGrouped>;
     int const rc = ensure_smem_attr(kernel, C::kSmemBytes, done);
