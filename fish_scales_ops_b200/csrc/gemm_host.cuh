@@ -4,7 +4,10 @@
 #include <atomic>
 #include <mutex>
 
+#include <cstdlib>
+
 #include "gemm.cuh"
+#include "gemm2.cuh"
 
 namespace fso {
 
@@ -137,6 +140,79 @@ inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmPa
     return launch_status("gemm_mxf8_kernel");
 }
 
+// Tensor map over a scale-word buffer seen as [atoms, 128] 32-bit words (one 512-byte atom per row), box = one atom.
+inline int make_sf_map(CUtensorMap* map, const void* base, int64_t atoms)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return FSO_ERR_UNSUPPORTED;
+    }
+    cuuint64_t const dims[2] = {128u, static_cast<cuuint64_t>(atoms)};
+    cuuint64_t const strides[1] = {512u};
+    cuuint32_t const box[2] = {128u, 1u};
+    cuuint32_t const estr[2] = {1u, 1u};
+    CUresult const r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (scale words) failed with CUresult %d", static_cast<int>(r));
+        return FSO_ERR_INTERNAL;
+    }
+    return 0;
+}
+
+// The CTA-pair kernel (gemm2.cuh) is opt-in: FSO_B200_PAIR=1 sends normal-orientation calls without split-K whose
+// 256 x 256 tiles fill the SM pairs to it (read once per process). It is bit-identical to the single-CTA kernel and
+// measured 4-6 % slower on B200, so the default keeps every call on the single-CTA kernel.
+inline bool pair_kernel_enabled()
+{
+    static int const v = [] {
+        const char* e = std::getenv("FSO_B200_PAIR");
+        return (e != nullptr && e[0] != '0' && e[0] != '\0') ? 1 : 0;
+    }();
+    return v != 0;
+}
+
+inline bool use_pair_kernel(int64_t m, int64_t n, int sms, bool swap, int splits)
+{
+    if (swap || splits != 1 || n % 256 != 0 || !pair_kernel_enabled()) return false;
+    int64_t const tiles = ((m + 255) / 256) * (n / 256);
+    return tiles >= sms / 2;
+}
+
+inline int launch_dense_pair(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m,
+    int64_t n, int64_t k, int sms, cudaStream_t stream)
+{
+    CUtensorMap ta, tb, tsa, tsb;
+    int rc;
+    int64_t const kb = k / 128;
+    if ((rc = make_operand_map(&ta, a, m, k, 128)) != 0) return rc;
+    if ((rc = make_operand_map(&tb, w, n, k, 128)) != 0) return rc;
+    if ((rc = make_sf_map(&tsa, sfa, (m + 127) / 128 * kb)) != 0) return rc;
+    if ((rc = make_sf_map(&tsb, sfw, n / 128 * kb)) != 0) return rc;
+    GemmParams p{};
+    p.out = d;
+    p.rows_a = static_cast<int>(m);
+    p.rows_b = static_cast<int>(n);
+    p.kb_total = static_cast<int>(kb);
+    p.kb_per_split = p.kb_total;
+    p.splits = 1;
+    p.tiles_a = static_cast<int>((m + 255) / 256);
+    p.tiles_b = static_cast<int>(n / 256);
+    p.group_a = p.tiles_a < 8 ? p.tiles_a : 8;
+    p.ldo = static_cast<int>(n);
+    p.out_rows = m;
+    p.out_align32 = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 ? 1 : 0;
+    int64_t const tiles = static_cast<int64_t>(p.tiles_a) * p.tiles_b;
+    int const pairs = static_cast<int>(tiles < sms / 2 ? tiles : sms / 2);
+    static std::atomic<uint64_t> done{0};
+    rc = ensure_smem_attr(gemm_mxf8_pair_kernel, Gemm2Cfg::kSmemBytes, done);
+    if (rc != 0) return rc;
+    gemm_mxf8_pair_kernel<<<2 * pairs, Gemm2Cfg::kThreads, Gemm2Cfg::kSmemBytes, stream>>>(ta, tb, tsa, tsb, p);
+    return launch_status("gemm_mxf8_pair_kernel");
+}
+
 // D[M, N] = A[M, K] * W[N, K]^T.
 inline int launch_dense(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
     int64_t k, void* ws, int64_t ws_bytes, cudaStream_t stream)
@@ -149,6 +225,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
             static_cast<long long>(ws_bytes));
         return FSO_ERR_INVALID;
     }
+    if (use_pair_kernel(m, n, sms, pl.swap, pl.splits)) return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
     CUtensorMap ta, tb;
     GemmParams p{};
     p.kb_total = static_cast<int>(k / 128);

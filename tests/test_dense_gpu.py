@@ -185,3 +185,66 @@ def test_run_to_run_identical_including_split_k(fso, device_ok):
     for m in (4, 128):
         x = inputs.activation(m, 8192, 2).cuda()
         assert torch.equal(fso.dense.linear(x, weight), fso.dense.linear(x, weight))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 28672, 4096), (128, 6144, 512), (200, 4096, 1024), (1024, 4096, 512),
+                                   (2000, 4096, 1024), (4096, 6144, 4096)])
+def test_bit_equal_to_cublas_block_scaled_gemm(fso, device_ok, m, n, k):
+    """cuBLAS's MXFP8 GEMM (`torch._scaled_mm` with E8M0 scales in the 32x4x4 swizzle, which is this library's atom
+    layout) is the kernel the reference itself sends every wide-N dense call to
+    (python/fish_scales_ops/gemm/_sm100_smm.py:273-306). Both accumulate K in order in fp32 inside the tensor core
+    and round once to bf16, so without split-K the outputs are equal bit for bit, whatever the tile shape (single
+    CTA, CTA pair, swapped orientation)."""
+    from fish_scales_ops_b200 import _ops
+
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    if e8 is None:
+        pytest.skip("this torch has no float8_e8m0fnu")
+    assert _ops.gemm_ws_bytes(m, n, k) == 0, "pick shapes that do not take the split-K route"
+    x = inputs.activation(m, k, 11 * m + k).cuda()
+    weight = fso.dense.prepare_weight(inputs.weight(n, k, 13 * n + k).cuda(), format="mxfp8")
+    xq, sx = fso.dense.quantize_activation(x)
+    y = fso.dense.linear(xq, weight, x_scale=sx)
+    try:
+        ref = torch._scaled_mm(xq, weight.weight.t(), scale_a=sx.view(torch.uint8).view(e8),
+                               scale_b=weight.scale.view(torch.uint8).view(e8), out_dtype=torch.bfloat16)
+    except Exception as exc:  # noqa: BLE001 - a torch / cuBLAS build without the MXFP8 recipe
+        pytest.skip(f"torch._scaled_mm does not serve MXFP8 here: {str(exc)[:120]}")
+    assert torch.equal(y, ref)
+
+
+def test_cta_pair_kernel_in_child_process(fso, device_ok):
+    """The opt-in CTA-pair kernel (FSO_B200_PAIR=1, read once per process, hence a child process) gives the bytes of
+    the single-CTA kernel, including a ragged M whose second CTA of the last pair has no rows."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import sys, torch
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+import inputs
+import fish_scales_ops_b200 as fso
+from fish_scales_ops_b200 import _ops
+for m, n, k in ((2048, 4096, 512), (1920, 5120, 256), (2100, 4096, 1024)):
+    x = inputs.activation(m, k, m + k).cuda()
+    w = fso.dense.prepare_weight(inputs.weight(n, k, n + k).cuda(), format="mxfp8")
+    torch.save(fso.dense.linear(x, w).cpu(), sys.argv[1] + f".{m}.pt")
+assert _ops.device_status() == 0
+print("ok")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tmp = os.path.join(root, "gpurun_out")
+    os.makedirs(tmp, exist_ok=True)
+    outs = {}
+    for pair in ("1", "0"):
+        env = dict(os.environ, FSO_B200_PAIR=pair)
+        base = os.path.join(tmp, f"pair{pair}")
+        res = subprocess.run([sys.executable, "-c", code % (root, os.path.join(root, "tests")), base], env=env,
+                             capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
+        outs[pair] = {m: torch.load(f"{base}.{m}.pt") for m in (2048, 1920, 2100)}
+        for m in (2048, 1920, 2100):
+            os.remove(f"{base}.{m}.pt")
+    for m in (2048, 1920, 2100):
+        assert torch.equal(outs["1"][m], outs["0"][m]), m
