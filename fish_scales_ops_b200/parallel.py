@@ -44,31 +44,36 @@ def expert_shard(num_experts: int, world: int, rank: int):
 
 @dataclasses.dataclass
 class DispatchPlan:
-    """What one rank sends where, for one batch. Row i of the send buffer is token ``send_token[i]``; the rows for
-    destination rank r are the contiguous range given by ``send_counts``."""
+    """What one rank sends where, for one batch. Row i of the send buffer is token ``send_token[i]`` bound for rank
+    ``send_rank[i]``; the rows for destination rank r are the contiguous range given by ``send_counts``."""
 
     send_token: torch.Tensor          # int64 [S]: source token of each sent row, grouped by destination rank
+    send_rank: torch.Tensor           # int64 [S]: destination rank of each sent row (non-decreasing)
     send_counts: list                 # python ints [G]
     recv_counts: list                 # python ints [G]
 
 
 def build_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
     """Which token goes to which rank: a token is sent to rank r when at least one of its top-k ids lies in r's
-    expert range (ids outside ``[0, E_global)`` belong to nobody). One small count exchange tells every rank how many
-    rows it will receive; this is the only host read in the exchange."""
+    expert range (ids outside ``[0, E_global)`` belong to nobody). Rows are grouped by destination rank with the
+    tokens ascending inside a group (deterministic). One small count exchange tells every rank how many rows it will
+    receive; its result is the only host read of the exchange."""
     t = int(topk_ids.shape[0])
     ids = topk_ids.to(torch.int64)
     valid = (ids >= 0) & (ids < experts_per_rank * world)
     owner = torch.where(valid, ids // experts_per_rank, torch.full_like(ids, -1))
     ranks = torch.arange(world, device=ids.device, dtype=torch.int64)
     needs = (owner.unsqueeze(-1) == ranks).any(dim=1)                      # [T, G]
-    # rows grouped by destination rank, tokens ascending inside a group (deterministic)
-    dest, tok = torch.nonzero(needs.t().contiguous(), as_tuple=True)        # sorted by rank, then token
+    flat = needs.t().reshape(-1)                                            # rank-major
+    # stable sort puts the needed (rank, token) pairs first, in rank-major / token-ascending order; no host read
+    order = torch.sort((~flat).to(torch.int8), stable=True).indices
     counts = needs.sum(dim=0).to(torch.int64)
     recv = torch.empty_like(counts)
     dist.all_to_all_single(recv, counts, group=group)
-    del dest, t
-    return DispatchPlan(tok, [int(v) for v in counts.tolist()], [int(v) for v in recv.tolist()])
+    both = torch.cat([counts, recv]).tolist()                               # the one host read
+    send_counts, recv_counts = [int(v) for v in both[:world]], [int(v) for v in both[world:]]
+    order = order[:sum(send_counts)]
+    return DispatchPlan(order % t, order // t, send_counts, recv_counts)
 
 
 def _a2a_rows(rows: torch.Tensor, in_counts, out_counts, group) -> torch.Tensor:
@@ -78,52 +83,60 @@ def _a2a_rows(rows: torch.Tensor, in_counts, out_counts, group) -> torch.Tensor:
     return out
 
 
+def _combine_partials(back: torch.Tensor, slot: torch.Tensor, ones: torch.Tensor) -> torch.Tensor:
+    """out[t] = bf16(sum over ranks r, ascending, of back[slot[t, r]]) with the library's combine kernel (fp32
+    accumulation in rank order, one rounding; slot -1 = no partial from that rank)."""
+    from . import _ops
+
+    out = torch.empty((slot.shape[0], back.shape[1]), dtype=torch.bfloat16, device=back.device)
+    if back.shape[0] == 0:
+        return out.zero_()
+    _ops.moe_combine(back, slot.reshape(-1), ones, None, None, out)
+    return out
+
+
 def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *,
-                          num_experts_global: int, group=None,
-                          layer_fn: Optional[Callable] = None) -> torch.Tensor:
+                          num_experts_global: int, group=None, layer_fn: Optional[Callable] = None,
+                          combine_fn: Optional[Callable] = None) -> torch.Tensor:
     """One MoE layer under expert parallelism: ``hidden`` bf16 ``[T, H]`` are this rank's tokens, ``topk_ids``
     ``[T, k]`` are GLOBAL expert ids, ``experts`` holds this rank's local experts. Returns the full result
     ``[T, H]`` for this rank's tokens (bf16), equal to the single-GPU layer over all experts up to the rounding of
-    the partial sums.
+    the per-rank partial sums.
 
-    ``layer_fn(hidden, experts, local_ids, weights)`` defaults to :func:`fish_scales_ops_b200.moe.layer`; the tests
-    of the exchange logic pass a CPU stand-in."""
+    ``layer_fn(hidden, experts, local_ids, weights)`` defaults to :func:`fish_scales_ops_b200.moe.layer` and
+    ``combine_fn(back, slot, ones)`` to the library's combine kernel; the CPU tests of the exchange logic pass
+    stand-ins for both."""
     if layer_fn is None:
         from . import moe
 
         layer_fn = moe.layer
+    if combine_fn is None:
+        combine_fn = _combine_partials
     world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
     if num_experts_global % world != 0:
         raise ValueError(f"expert_parallel_layer: {num_experts_global} experts over {world} ranks")
     per = num_experts_global // world
-    t, h = int(hidden.shape[0]), int(hidden.shape[1])
+    t, k = int(hidden.shape[0]), int(topk_ids.shape[1])
     plan = build_dispatch(topk_ids, per, world, group)
 
-    # dispatch: token rows, their ids and their weights
+    # dispatch: token rows, and (ids localized for the destination rank | weights) packed into one int32 tensor
     send_rows = hidden.index_select(0, plan.send_token)
-    send_ids = topk_ids.to(torch.int32).index_select(0, plan.send_token)
-    send_w = topk_w.to(torch.float32).index_select(0, plan.send_token)
+    ids_sel = topk_ids.to(torch.int64).index_select(0, plan.send_token)
+    lo = (plan.send_rank * per).unsqueeze(1)
+    local_ids = torch.where((ids_sel >= lo) & (ids_sel < lo + per), ids_sel - lo, torch.full_like(ids_sel, -1))
+    meta = torch.cat([local_ids.to(torch.int32),
+                      topk_w.to(torch.float32).index_select(0, plan.send_token).view(torch.int32)], dim=1)
     recv_rows = _a2a_rows(send_rows, plan.send_counts, plan.recv_counts, group)
-    recv_ids = _a2a_rows(send_ids, plan.send_counts, plan.recv_counts, group)
-    recv_w = _a2a_rows(send_w, plan.send_counts, plan.recv_counts, group)
-
-    # local experts only: everybody else's ids become -1, mine become local indices
-    lo = rank * per
-    mine = (recv_ids >= lo) & (recv_ids < lo + per)
-    local_ids = torch.where(mine, recv_ids - lo, torch.full_like(recv_ids, -1))
-    partial = layer_fn(recv_rows, experts, local_ids, recv_w)
+    recv_meta = _a2a_rows(meta, plan.send_counts, plan.recv_counts, group)
+    partial = layer_fn(recv_rows, experts, recv_meta[:, :k].contiguous(),
+                       recv_meta[:, k:].contiguous().view(torch.float32))
 
     # combine: partial rows go back to their source rank, which adds them in rank order (fp32, one rounding)
     back = _a2a_rows(partial, plan.recv_counts, plan.send_counts, group)
-    out = torch.zeros((t, h), dtype=torch.float32, device=hidden.device)
-    start = 0
-    for r in range(world):
-        n = plan.send_counts[r]
-        if n:
-            out.index_add_(0, plan.send_token[start:start + n], back[start:start + n].to(torch.float32))
-        start += n
-    return out.to(torch.bfloat16)
+    slot = torch.full((t, world), -1, dtype=torch.int32, device=hidden.device)
+    slot[plan.send_token, plan.send_rank] = torch.arange(back.shape[0], dtype=torch.int32, device=hidden.device)
+    ones = torch.ones((t, world), dtype=torch.float32, device=hidden.device)
+    return combine_fn(back, slot, ones)
 
 
 def dispatch_bytes(plan: DispatchPlan, rank: int, hidden_size: int, topk: int) -> int:

@@ -42,6 +42,15 @@ def _layer_cpu(hidden, experts, ids, wts):
     return out.to(torch.bfloat16)
 
 
+def _combine_cpu(back, slot, ones):
+    """Stand-in for the combine kernel: fp32 sum of the partial rows in rank order, one rounding to bf16."""
+    out = torch.zeros(slot.shape[0], back.shape[1])
+    for r in range(slot.shape[1]):
+        sel = slot[:, r] >= 0
+        out[sel] += back[slot[sel, r].long()].float()
+    return out.to(torch.bfloat16)
+
+
 def _batch(rank):
     hidden = inputs.activation(T + rank, H, 100 + rank)
     ids, wts = inputs.routing(T + rank, E, K, 200 + rank)
@@ -64,7 +73,7 @@ def _worker(rank, world, port, ret):
         hidden, ids, wts = _batch(rank)
         plan = parallel.build_dispatch(ids, E // world, world)
         out = parallel.expert_parallel_layer(hidden, (w13[e0:e1], w2[e0:e1]), ids, wts, num_experts_global=E,
-                                             layer_fn=_layer_cpu)
+                                             layer_fn=_layer_cpu, combine_fn=_combine_cpu)
         ret[rank] = (out, plan.send_counts, plan.recv_counts, parallel.dispatch_bytes(plan, rank, H, K))
     finally:
         dist.destroy_process_group()
