@@ -274,6 +274,13 @@ int fso_moe_gather_quant(const void* hidden, const int32_t* slot_of_flat, int64_
     constexpr int kUnroll = 2;
     int const kb = static_cast<int>(h / 128);
     FSO_REQUIRE(tokens * kb < (1ll << 31) - 4096, "fso_moe_gather_quant: tokens * H/128 is beyond the kernel's index range");
+    if ((reinterpret_cast<uintptr_t>(hidden) & 31u) == 0) {
+        int64_t const octs = (tokens * kb + kUnroll - 1) / kUnroll;
+        gather_quant_wide_kernel<kUnroll><<<static_cast<unsigned>((octs * 8 + 255) / 256), 256, 0, as_stream(stream)>>>(
+            static_cast<const uint8_t*>(hidden), slot_of_flat, tokens, static_cast<int>(topk), kb,
+            static_cast<uint4*>(hq), static_cast<uint32_t*>(sh));
+        return launch_status("gather_quant_wide_kernel");
+    }
     int64_t const halves = (tokens * kb + kUnroll - 1) / kUnroll;
     int64_t const blocks = (halves * 16 + 255) / 256;
     gather_quant_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
@@ -331,6 +338,27 @@ int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* to
     int const h8 = static_cast<int>(h / 8);
     int64_t const total = tokens * h8;
     FSO_REQUIRE(total < (1ll << 31) - 4096, "fso_moe_combine: tokens * H/8 is beyond the kernel's index range");
+    bool const wide_ok = ((reinterpret_cast<uintptr_t>(dn) | reinterpret_cast<uintptr_t>(out)
+                              | reinterpret_cast<uintptr_t>(bias)) & 31u) == 0 && topk <= 8;
+    int const groups = topk <= 2 ? 4 : topk <= 4 ? 2 : 1;
+    if (wide_ok && h % (16 * groups) == 0) {
+        int64_t const threads = tokens * (h / (16 * groups));
+        unsigned const blocks = static_cast<unsigned>((threads + 255) / 256);
+        auto* dnb = static_cast<const uint8_t*>(dn);
+        auto* bb = static_cast<const uint8_t*>(bias);
+        auto* ob = static_cast<uint8_t*>(out);
+        int const hb = static_cast<int>(h * 2);
+        if (groups == 4)
+            combine_wide_kernel<2, 4><<<blocks, 256, 0, as_stream(stream)>>>(dnb, slot_of_flat, topk_w, bb, bias_scale, ob,
+                tokens, static_cast<int>(topk), hb);
+        else if (topk <= 4)
+            combine_wide_kernel<4, 2><<<blocks, 256, 0, as_stream(stream)>>>(dnb, slot_of_flat, topk_w, bb, bias_scale, ob,
+                tokens, static_cast<int>(topk), hb);
+        else
+            combine_wide_kernel<8, 1><<<blocks, 256, 0, as_stream(stream)>>>(dnb, slot_of_flat, topk_w, bb, bias_scale, ob,
+                tokens, static_cast<int>(topk), hb);
+        return launch_status("combine_wide_kernel");
+    }
     combine_kernel<8><<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
         static_cast<const uint4*>(dn), slot_of_flat, topk_w, static_cast<const uint4*>(bias), bias_scale,
         static_cast<uint4*>(out), tokens, static_cast<int>(topk), h8);

@@ -198,6 +198,44 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(const uint4* __restri
     }
 }
 
+// The same with 16 elements per thread (256-bit loads, 128-bit stores, 8 lanes per chunk); needs a 32-byte aligned
+// hidden tensor.
+template <int kUnroll>
+__global__ void __launch_bounds__(256) gather_quant_wide_kernel(const uint8_t* __restrict__ hidden,
+    const int32_t* __restrict__ slot_of_flat, int64_t tokens, int topk, int kb, uint4* __restrict__ hq,
+    uint32_t* __restrict__ sh)
+{
+    uint32_t const sub = threadIdx.x & 7;
+    uint32_t const oct = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    uint32_t const total = static_cast<uint32_t>(tokens) * static_cast<uint32_t>(kb);
+    uint32_t v[kUnroll][8];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        uint32_t const c = oct * kUnroll + u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[u][i] = 0;
+        if (c < total) ld_nc_256(hidden + (static_cast<size_t>(c) * 8 + sub) * 32, v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        uint32_t const c = oct * kUnroll + u;
+        uint4 codes;
+        uint32_t const byte = quant16_shared2(v[u], codes);
+        uint32_t const word = word_from_8lanes(byte, sub);
+        if (c < total) {
+            uint32_t const t = c / static_cast<uint32_t>(kb);
+            int const kp = static_cast<int>(c - t * kb);
+            for (int j = 0; j < topk; ++j) {
+                int const slot = __ldg(slot_of_flat + static_cast<size_t>(t) * topk + j);
+                if (slot >= 0) {
+                    hq[(static_cast<int64_t>(slot) * kb + kp) * 8 + sub] = codes;
+                    if (sub == 0) sh[sf_word_index(slot, kp, kb)] = word;
+                }
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- combine
 
 // One (token, 8 columns) per thread: fp32 FMA chain over the token's top-k rows in ascending j, then the bias term,
@@ -252,6 +290,69 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
     o.z = pack_bf16x2(acc[4], acc[5]);
     o.w = pack_bf16x2(acc[6], acc[7]);
     out[idx] = o;
+}
+
+// The combine with 256-bit accesses: one thread owns kGroups x 16 columns of one token, so that about eight 32-byte
+// row loads are in flight per thread whatever the top-k (top-2 -> 4 groups, top-8 -> 1 group). Same arithmetic and
+// order as combine_kernel. Needs 32-byte aligned dn / out / bias and H % (16 * kGroups) == 0.
+template <int kMaxTopk, int kGroups>
+__global__ void __launch_bounds__(256) combine_wide_kernel(const uint8_t* __restrict__ dn,
+    const int32_t* __restrict__ slot_of_flat, const float* __restrict__ topk_w, const uint8_t* __restrict__ bias,
+    const float* __restrict__ bias_scale, uint8_t* __restrict__ out, int64_t tokens, int topk, int h_bytes)
+{
+    constexpr int kSpan = 32 * kGroups;                      // bytes of one row this thread owns
+    uint32_t const per_row = static_cast<uint32_t>(h_bytes) / kSpan;
+    uint32_t const idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<uint32_t>(tokens) * per_row) return;
+    uint32_t const t32 = idx / per_row;
+    size_t const col = static_cast<size_t>(idx - t32 * per_row) * kSpan;
+    int64_t const t = t32;
+    float acc[16 * kGroups];
+#pragma unroll
+    for (int i = 0; i < 16 * kGroups; ++i) acc[i] = 0.f;
+    auto fma_row = [&](uint32_t const (&raw)[8], float w, int g) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            acc[g * 16 + 2 * i] = fmaf(w, __uint_as_float(raw[i] << 16), acc[g * 16 + 2 * i]);
+            acc[g * 16 + 2 * i + 1] = fmaf(w, __uint_as_float(raw[i] & 0xFFFF0000u), acc[g * 16 + 2 * i + 1]);
+        }
+    };
+    int slots[kMaxTopk];
+    float ws[kMaxTopk];
+#pragma unroll
+    for (int j = 0; j < kMaxTopk; ++j) {
+        slots[j] = j < topk ? __ldg(slot_of_flat + t * topk + j) : -1;
+        ws[j] = j < topk ? __ldg(topk_w + t * topk + j) : 0.f;
+    }
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g) {
+        uint32_t raw[kMaxTopk][8];
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (slots[j] >= 0) ld_nc_256(dn + static_cast<size_t>(slots[j]) * h_bytes + col + 32 * g, raw[j]);
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (slots[j] >= 0) fma_row(raw[j], ws[j], g);
+    }
+    if (bias != nullptr) {
+        float const bs = bias_scale != nullptr ? __ldg(bias_scale + t) : 1.f;
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g) {
+            uint32_t raw[8];
+            ld_nc_256(bias + static_cast<size_t>(t) * h_bytes + col + 32 * g, raw);
+            fma_row(raw, bs, g);
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g) {
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = pack_bf16x2(acc[g * 16 + 2 * i], acc[g * 16 + 2 * i + 1]);
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"l"(out + static_cast<size_t>(t) * h_bytes + col + 32 * g), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                     "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                     : "memory");
+    }
 }
 
 }  // namespace fso

@@ -14,6 +14,7 @@ cover the two ways the path shards:
 Kernels only ever read this GPU's memory: rows arrive through NCCL before any kernel touches them.
 """
 import dataclasses
+import os
 from typing import Callable, Optional
 
 import torch
@@ -95,13 +96,25 @@ def _combine_partials(back: torch.Tensor, slot: torch.Tensor, ones: torch.Tensor
     return out
 
 
+def _a2a_rows_async(rows: torch.Tensor, in_counts, out_counts, group):
+    out = rows.new_empty((sum(out_counts),) + tuple(rows.shape[1:]))
+    work = dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(out_counts),
+                                  input_split_sizes=list(in_counts), group=group, async_op=True)
+    return out, work
+
+
 def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *,
                           num_experts_global: int, group=None, layer_fn: Optional[Callable] = None,
-                          combine_fn: Optional[Callable] = None) -> torch.Tensor:
+                          combine_fn: Optional[Callable] = None, micro_batches: Optional[int] = None) -> torch.Tensor:
     """One MoE layer under expert parallelism: ``hidden`` bf16 ``[T, H]`` are this rank's tokens, ``topk_ids``
     ``[T, k]`` are GLOBAL expert ids, ``experts`` holds this rank's local experts. Returns the full result
     ``[T, H]`` for this rank's tokens (bf16), equal to the single-GPU layer over all experts up to the rounding of
     the per-rank partial sums.
+
+    The tokens are processed in ``micro_batches`` slices (default 1; the environment variable
+    ``FSO_B200_EP_MICRO_BATCHES`` overrides the default) whose exchanges are
+    issued asynchronously: while the grouped GEMMs of one slice run, the next slice's dispatch and the previous
+    slice's combine are on the wire.
 
     ``layer_fn(hidden, experts, local_ids, weights)`` defaults to :func:`fish_scales_ops_b200.moe.layer` and
     ``combine_fn(back, slot, ones)`` to the library's combine kernel; the CPU tests of the exchange logic pass
@@ -117,26 +130,53 @@ def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor,
         raise ValueError(f"expert_parallel_layer: {num_experts_global} experts over {world} ranks")
     per = num_experts_global // world
     t, k = int(hidden.shape[0]), int(topk_ids.shape[1])
-    plan = build_dispatch(topk_ids, per, world, group)
+    if micro_batches is None:
+        env = os.environ.get("FSO_B200_EP_MICRO_BATCHES", "")
+        # slicing streams the local experts' weights once per slice and shrinks every kernel; measured slower than
+        # one slice on 2 GPUs (2.90 -> 4.10 ms) and on 4 GPUs (3.15 -> 3.86 ms), so one slice is the default
+        micro_batches = int(env) if env.isdigit() and int(env) > 0 else 1
+    micro_batches = max(1, min(int(micro_batches), max(1, t)))
+    bounds = [t * i // micro_batches for i in range(micro_batches + 1)]
+    out = torch.empty((t, int(hidden.shape[1])), dtype=torch.bfloat16, device=hidden.device)
 
-    # dispatch: token rows, and (ids localized for the destination rank | weights) packed into one int32 tensor
-    send_rows = hidden.index_select(0, plan.send_token)
-    ids_sel = topk_ids.to(torch.int64).index_select(0, plan.send_token)
-    lo = (plan.send_rank * per).unsqueeze(1)
-    local_ids = torch.where((ids_sel >= lo) & (ids_sel < lo + per), ids_sel - lo, torch.full_like(ids_sel, -1))
-    meta = torch.cat([local_ids.to(torch.int32),
-                      topk_w.to(torch.float32).index_select(0, plan.send_token).view(torch.int32)], dim=1)
-    recv_rows = _a2a_rows(send_rows, plan.send_counts, plan.recv_counts, group)
-    recv_meta = _a2a_rows(meta, plan.send_counts, plan.recv_counts, group)
-    partial = layer_fn(recv_rows, experts, recv_meta[:, :k].contiguous(),
-                       recv_meta[:, k:].contiguous().view(torch.float32))
+    # stage 1: plan every slice and put its dispatch on the wire (token rows; ids localized for the destination rank
+    # and weights packed into one int32 tensor)
+    slices = []
+    for i in range(micro_batches):
+        t0, t1 = bounds[i], bounds[i + 1]
+        ids_i, w_i = topk_ids[t0:t1], topk_w[t0:t1]
+        plan = build_dispatch(ids_i, per, world, group)
+        send_rows = hidden[t0:t1].index_select(0, plan.send_token)
+        ids_sel = ids_i.to(torch.int64).index_select(0, plan.send_token)
+        lo = (plan.send_rank * per).unsqueeze(1)
+        local_ids = torch.where((ids_sel >= lo) & (ids_sel < lo + per), ids_sel - lo, torch.full_like(ids_sel, -1))
+        meta = torch.cat([local_ids.to(torch.int32),
+                          w_i.to(torch.float32).index_select(0, plan.send_token).view(torch.int32)], dim=1)
+        recv_rows, w_rows = _a2a_rows_async(send_rows, plan.send_counts, plan.recv_counts, group)
+        recv_meta, w_meta = _a2a_rows_async(meta, plan.send_counts, plan.recv_counts, group)
+        slices.append(dict(t0=t0, t1=t1, plan=plan, recv_rows=recv_rows, recv_meta=recv_meta, works=(w_rows, w_meta),
+                           keep=(send_rows, meta)))
 
-    # combine: partial rows go back to their source rank, which adds them in rank order (fp32, one rounding)
-    back = _a2a_rows(partial, plan.recv_counts, plan.send_counts, group)
-    slot = torch.full((t, world), -1, dtype=torch.int32, device=hidden.device)
-    slot[plan.send_token, plan.send_rank] = torch.arange(back.shape[0], dtype=torch.int32, device=hidden.device)
-    ones = torch.ones((t, world), dtype=torch.float32, device=hidden.device)
-    return combine_fn(back, slot, ones)
+    # stage 2: local experts of each slice, its partial rows go back asynchronously
+    for sl in slices:
+        for w in sl["works"]:
+            w.wait()
+        meta = sl["recv_meta"]
+        partial = layer_fn(sl["recv_rows"], experts, meta[:, :k].contiguous(),
+                           meta[:, k:].contiguous().view(torch.float32))
+        sl["back"], sl["work_back"] = _a2a_rows_async(partial, sl["plan"].recv_counts, sl["plan"].send_counts, group)
+        sl["keep"] = (partial,)
+
+    # stage 3: the source rank adds a token's partial rows in rank order (fp32, one rounding)
+    for sl in slices:
+        sl["work_back"].wait()
+        plan, n = sl["plan"], sl["t1"] - sl["t0"]
+        slot = torch.full((n, world), -1, dtype=torch.int32, device=hidden.device)
+        slot[plan.send_token, plan.send_rank] = torch.arange(sl["back"].shape[0], dtype=torch.int32,
+                                                            device=hidden.device)
+        ones = torch.ones((n, world), dtype=torch.float32, device=hidden.device)
+        out[sl["t0"]:sl["t1"]] = combine_fn(sl["back"], slot, ones)
+    return out
 
 
 def dispatch_bytes(plan: DispatchPlan, rank: int, hidden_size: int, topk: int) -> int:

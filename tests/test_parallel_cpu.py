@@ -74,6 +74,9 @@ def _worker(rank, world, port, ret):
         plan = parallel.build_dispatch(ids, E // world, world)
         out = parallel.expert_parallel_layer(hidden, (w13[e0:e1], w2[e0:e1]), ids, wts, num_experts_global=E,
                                              layer_fn=_layer_cpu, combine_fn=_combine_cpu)
+        out3 = parallel.expert_parallel_layer(hidden, (w13[e0:e1], w2[e0:e1]), ids, wts, num_experts_global=E,
+                                              layer_fn=_layer_cpu, combine_fn=_combine_cpu, micro_batches=3)
+        assert torch.equal(out, out3), "slicing the tokens into micro-batches must not change a single byte"
         ret[rank] = (out, plan.send_counts, plan.recv_counts, parallel.dispatch_bytes(plan, rank, H, K))
     finally:
         dist.destroy_process_group()

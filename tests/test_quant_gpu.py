@@ -93,3 +93,22 @@ def test_quantizer_is_run_to_run_identical(fso, device_ok):
     a = _ops.quantize_1x32_fp8(x)
     b = _ops.quantize_1x32_fp8(x)
     assert torch.equal(a[0].view(torch.uint8), b[0].view(torch.uint8)) and torch.equal(a[1], b[1])
+
+
+def test_quantizer_narrow_and_wide_kernels_agree(fso, oracle, device_ok):
+    """A 32-byte aligned input takes the 256-bit-load kernel, a 16-byte aligned one the 128-bit-load kernel; both
+    give the oracle's bytes."""
+    from fish_scales_ops_b200 import _ops
+
+    m, k = 300, 640
+    x = inputs.activation(m, k, 41)
+    buf = torch.zeros(m * k + 8, dtype=torch.bfloat16, device="cuda")
+    buf[8:] = x.reshape(-1).cuda()
+    narrow = buf[8:].view(m, k)
+    assert narrow.data_ptr() % 32 == 16 and narrow.is_contiguous()
+    wide = x.cuda()
+    assert wide.data_ptr() % 32 == 0
+    oq, os_ = oracle.quantize_1x32(x)
+    for t in (narrow, wide):
+        q, s = _ops.quantize_1x32_fp8(t)
+        assert np.array_equal(inputs.to_np_u8(q), oq) and np.array_equal(inputs.to_np_u32(s), os_)
