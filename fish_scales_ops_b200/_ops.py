@@ -154,5 +154,31 @@ def moe_combine(dn, slot, topk_w, bias, bias_scale, out):
                                     stream_ptr()), "fso_moe_combine")
 
 
+def ep_dispatch_push(xq, xs, topk_ids, topk_w, send_token, send_rank, send_off, dst_base, peer_q, peer_w, peer_ids,
+                     peer_wt, experts_per_rank: int):
+    """Store this rank's sent rows into the destination ranks' receive buffers (peer-mapped addresses)."""
+    rows, topk, h = int(send_token.shape[0]), int(topk_ids.shape[1]), int(xq.shape[1])
+    with torch.cuda.device(xq.device):
+        check(lib().fso_ep_dispatch_push(ptr(xq), ptr(xs), ptr(topk_ids), ptr(topk_w), ptr(send_token), ptr(send_rank),
+                                         ptr(send_off), ptr(dst_base), ptr(peer_q), ptr(peer_w), ptr(peer_ids),
+                                         ptr(peer_wt), rows, topk, h, int(experts_per_rank), stream_ptr()),
+              "fso_ep_dispatch_push")
+
+
+def moe_gather_rows(rx_q, rx_w, slot, topk: int, hq, sh):
+    rows_in, h = int(rx_q.shape[0]), int(rx_q.shape[1])
+    with torch.cuda.device(rx_q.device):
+        check(lib().fso_moe_gather_rows(ptr(rx_q), ptr(rx_w), ptr(slot), rows_in, topk, h, int(hq.shape[0]), ptr(hq),
+                                        ptr(sh), stream_ptr()), "fso_moe_gather_rows")
+
+
+def moe_combine_scatter(dn, slot, topk_w, recv_off, back_base, peer_back, world: int):
+    tokens, topk, h = int(topk_w.shape[0]), int(topk_w.shape[1]), int(dn.shape[1])
+    with torch.cuda.device(dn.device):
+        check(lib().fso_moe_combine_scatter(ptr(dn), ptr(slot), ptr(topk_w), tokens, topk, h, ptr(recv_off),
+                                            ptr(back_base), ptr(peer_back), int(world), stream_ptr()),
+              "fso_moe_combine_scatter")
+
+
 def device_status() -> int:
     return _lib.device_status()

@@ -39,6 +39,7 @@ int sm_count()
 
 #include "gemm_host.cuh"
 #include "moe.cuh"
+#include "exchange.cuh"
 
 using namespace fso;
 
@@ -326,18 +327,13 @@ int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2,
         as_stream(stream));
 }
 
-int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,
-    const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, void* stream)
+static int launch_combine(const char* op, const void* dn, const int32_t* slot_of_flat, const float* topk_w,
+    const void* bias, const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, RowScatter sc,
+    void* stream)
 {
-    FSO_REQUIRE(tokens >= 0 && topk >= 1 && h > 0 && h % 8 == 0, "fso_moe_combine: H must be a multiple of 8");
-    if (tokens == 0) return 0;
-    FSO_REQUIRE(dn && slot_of_flat && topk_w && out, "fso_moe_combine: NULL pointer");
-    FSO_REQUIRE(aligned16(dn) && aligned16(out) && (bias == nullptr || aligned16(bias)),
-        "fso_moe_combine: dn, out and bias must be 16-byte aligned");
-    FSO_REQUIRE(bias != nullptr || bias_scale == nullptr, "fso_moe_combine: bias_scale scales bias and needs it");
     int const h8 = static_cast<int>(h / 8);
     int64_t const total = tokens * h8;
-    FSO_REQUIRE(total < (1ll << 31) - 4096, "fso_moe_combine: tokens * H/8 is beyond the kernel's index range");
+    FSO_REQUIRE(total < (1ll << 31) - 4096, "%s: tokens * H/8 is beyond the kernel's index range", op);
     bool const wide_ok = ((reinterpret_cast<uintptr_t>(dn) | reinterpret_cast<uintptr_t>(out)
                               | reinterpret_cast<uintptr_t>(bias)) & 31u) == 0 && topk <= 8;
     int const groups = topk <= 2 ? 4 : topk <= 4 ? 2 : 1;
@@ -350,19 +346,82 @@ int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* to
         int const hb = static_cast<int>(h * 2);
         if (groups == 4)
             combine_wide_kernel<2, 4><<<blocks, 256, 0, as_stream(stream)>>>(dnb, slot_of_flat, topk_w, bb, bias_scale, ob,
-                tokens, static_cast<int>(topk), hb);
+                tokens, static_cast<int>(topk), hb, sc);
         else if (topk <= 4)
             combine_wide_kernel<4, 2><<<blocks, 256, 0, as_stream(stream)>>>(dnb, slot_of_flat, topk_w, bb, bias_scale, ob,
-                tokens, static_cast<int>(topk), hb);
+                tokens, static_cast<int>(topk), hb, sc);
         else
             combine_wide_kernel<8, 1><<<blocks, 256, 0, as_stream(stream)>>>(dnb, slot_of_flat, topk_w, bb, bias_scale, ob,
-                tokens, static_cast<int>(topk), hb);
+                tokens, static_cast<int>(topk), hb, sc);
         return launch_status("combine_wide_kernel");
     }
+    FSO_REQUIRE(sc.world == 0, "%s: needs 32-byte aligned rows, H a multiple of 64 and top-k <= 8", op);
     combine_kernel<8><<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
         static_cast<const uint4*>(dn), slot_of_flat, topk_w, static_cast<const uint4*>(bias), bias_scale,
         static_cast<uint4*>(out), tokens, static_cast<int>(topk), h8);
     return launch_status("combine_kernel");
+}
+
+int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,
+    const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, void* stream)
+{
+    FSO_REQUIRE(tokens >= 0 && topk >= 1 && h > 0 && h % 8 == 0, "fso_moe_combine: H must be a multiple of 8");
+    if (tokens == 0) return 0;
+    FSO_REQUIRE(dn && slot_of_flat && topk_w && out, "fso_moe_combine: NULL pointer");
+    FSO_REQUIRE(aligned16(dn) && aligned16(out) && (bias == nullptr || aligned16(bias)),
+        "fso_moe_combine: dn, out and bias must be 16-byte aligned");
+    FSO_REQUIRE(bias != nullptr || bias_scale == nullptr, "fso_moe_combine: bias_scale scales bias and needs it");
+    return launch_combine("fso_moe_combine", dn, slot_of_flat, topk_w, bias, bias_scale, out, tokens, topk, h,
+        RowScatter{nullptr, nullptr, nullptr, 0}, stream);
+}
+
+int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const float* topk_w, int64_t tokens,
+    int64_t topk, int64_t h, const int64_t* recv_off, const int64_t* back_base, const uint64_t* peer_back,
+    int64_t world, void* stream)
+{
+    FSO_REQUIRE(tokens >= 0 && topk >= 1 && topk <= 8 && h > 0 && h % 64 == 0 && world >= 1 && world <= 1024,
+        "fso_moe_combine_scatter: 1 <= top-k <= 8, H a multiple of 64 and 1 <= world <= 1024 required");
+    if (tokens == 0) return 0;
+    FSO_REQUIRE(dn && slot_of_flat && topk_w && recv_off && back_base && peer_back,
+        "fso_moe_combine_scatter: NULL pointer");
+    FSO_REQUIRE((reinterpret_cast<uintptr_t>(dn) & 31u) == 0, "fso_moe_combine_scatter: dn must be 32-byte aligned");
+    return launch_combine("fso_moe_combine_scatter", dn, slot_of_flat, topk_w, nullptr, nullptr, nullptr, tokens, topk,
+        h, RowScatter{recv_off, back_base, peer_back, static_cast<int>(world)}, stream);
+}
+
+int fso_ep_dispatch_push(const void* xq, const void* xs, const int32_t* topk_ids, const float* topk_w,
+    const int64_t* send_token, const int64_t* send_rank, const int64_t* send_off, const int64_t* dst_base,
+    const uint64_t* peer_q, const uint64_t* peer_w, const uint64_t* peer_ids, const uint64_t* peer_wt, int64_t rows,
+    int64_t topk, int64_t h, int64_t experts_per_rank, void* stream)
+{
+    FSO_REQUIRE(rows >= 0 && rows < (1ll << 31) && topk >= 1 && topk <= 128 && h > 0 && h % 128 == 0
+            && experts_per_rank >= 1 && experts_per_rank < (1ll << 31),
+        "fso_ep_dispatch_push: H a multiple of 128 and 1 <= top-k <= 128 required");
+    if (rows == 0) return 0;
+    FSO_REQUIRE(xq && xs && topk_ids && topk_w && send_token && send_rank && send_off && dst_base && peer_q && peer_w
+            && peer_ids && peer_wt, "fso_ep_dispatch_push: NULL pointer");
+    FSO_REQUIRE(aligned16(xq), "fso_ep_dispatch_push: xq must be 16-byte aligned");
+    ep_push_rows_kernel<<<static_cast<unsigned>(rows), 128, 0, as_stream(stream)>>>(static_cast<const uint4*>(xq),
+        static_cast<const uint32_t*>(xs), topk_ids, topk_w, send_token, send_rank, send_off, dst_base, peer_q, peer_w,
+        peer_ids, peer_wt, static_cast<int>(topk), static_cast<int>(h / 128), static_cast<int>(experts_per_rank));
+    return launch_status("ep_push_rows_kernel");
+}
+
+int fso_moe_gather_rows(const void* rx_q, const void* rx_w, const int32_t* slot_of_flat, int64_t rows_in, int64_t topk,
+    int64_t h, int64_t rows, void* hq, void* sh, void* stream)
+{
+    FSO_REQUIRE(rows_in >= 0 && topk >= 1 && h > 0 && h % 128 == 0 && rows > 0 && rows % 128 == 0,
+        "fso_moe_gather_rows: H a multiple of 128 and rows a multiple of 128 required");
+    if (rows_in == 0) return 0;
+    FSO_REQUIRE(rx_q && rx_w && slot_of_flat && hq && sh, "fso_moe_gather_rows: NULL pointer");
+    FSO_REQUIRE(aligned16(rx_q) && aligned16(hq) && (reinterpret_cast<uintptr_t>(sh) & 3u) == 0
+            && (reinterpret_cast<uintptr_t>(rx_w) & 3u) == 0, "fso_moe_gather_rows: rx_q and hq must be 16-byte aligned");
+    int64_t const total = rows_in * (h / 16);
+    FSO_REQUIRE(total < (1ll << 31) - 4096, "fso_moe_gather_rows: rows * H/16 is beyond the kernel's index range");
+    gather_rows_q_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+        static_cast<const uint4*>(rx_q), static_cast<const uint32_t*>(rx_w), slot_of_flat, rows_in,
+        static_cast<int>(topk), static_cast<int>(h / 128), static_cast<uint4*>(hq), static_cast<uint32_t*>(sh));
+    return launch_status("gather_rows_q_kernel");
 }
 
 }  // extern "C"

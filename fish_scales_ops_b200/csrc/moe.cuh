@@ -292,13 +292,24 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
     out[idx] = o;
 }
 
+// Where the combine's output rows go when they are not one dense [tokens, H] tensor: token t, which lies in
+// [recv_off[s], recv_off[s + 1]) for exactly one s < world, is written to row back_base[s] + (t - recv_off[s]) of the
+// bf16 [*, H] buffer at address peer_back[s] (another GPU's memory under expert parallelism). world == 0: dense.
+struct RowScatter {
+    const int64_t* recv_off;
+    const int64_t* back_base;
+    const uint64_t* peer_back;
+    int world;
+};
+
 // The combine with 256-bit accesses: one thread owns kGroups x 16 columns of one token, so that about eight 32-byte
 // row loads are in flight per thread whatever the top-k (top-2 -> 4 groups, top-8 -> 1 group). Same arithmetic and
 // order as combine_kernel. Needs 32-byte aligned dn / out / bias and H % (16 * kGroups) == 0.
 template <int kMaxTopk, int kGroups>
 __global__ void __launch_bounds__(256) combine_wide_kernel(const uint8_t* __restrict__ dn,
     const int32_t* __restrict__ slot_of_flat, const float* __restrict__ topk_w, const uint8_t* __restrict__ bias,
-    const float* __restrict__ bias_scale, uint8_t* __restrict__ out, int64_t tokens, int topk, int h_bytes)
+    const float* __restrict__ bias_scale, uint8_t* __restrict__ out, int64_t tokens, int topk, int h_bytes,
+    RowScatter sc)
 {
     constexpr int kSpan = 32 * kGroups;                      // bytes of one row this thread owns
     uint32_t const per_row = static_cast<uint32_t>(h_bytes) / kSpan;
@@ -343,16 +354,24 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const uint8_t* __rest
             fma_row(raw, bs, g);
         }
     }
+    uint8_t* out_row = out + static_cast<size_t>(t) * h_bytes;
+    if (sc.world > 0) {
+        int s = 0;
+        while (s + 1 < sc.world && t >= __ldg(sc.recv_off + s + 1)) ++s;
+        out_row = reinterpret_cast<uint8_t*>(__ldg(sc.peer_back + s))
+                  + static_cast<size_t>(__ldg(sc.back_base + s) + (t - __ldg(sc.recv_off + s))) * h_bytes;
+    }
 #pragma unroll
     for (int g = 0; g < kGroups; ++g) {
         uint32_t o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = pack_bf16x2(acc[g * 16 + 2 * i], acc[g * 16 + 2 * i + 1]);
         asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"l"(out + static_cast<size_t>(t) * h_bytes + col + 32 * g), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                     ::"l"(out_row + col + 32 * g), "r"(o[0]), "r"(o[1]), "r"(o[2]),
                      "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
                      : "memory");
     }
+    if (sc.world > 0) __threadfence_system();
 }
 
 }  // namespace fso

@@ -291,6 +291,38 @@ def _run_layer(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale):
     return out
 
 
+def _run_layer_rows(rx_q, rx_w, experts, topk_ids, topk_w, recv_off, back_base, peer_back, world):
+    """The layer over rows that arrive already quantized and whose result rows leave for other buffers: the
+    expert-parallel form. ``rx_q`` e4m3 codes ``[R, H]`` and ``rx_w`` int32 scale words ``[R, H/128]`` (row-major, as
+    the sending rank's dispatch kernel stored them), ``topk_ids`` int32 ``[R, k]`` local expert ids (-1 = another
+    rank's expert), ``topk_w`` fp32 ``[R, k]``. Result row t is written by the combine kernel to row
+    ``back_base[s] + (t - recv_off[s])`` of the bf16 buffer at address ``peer_back[s]`` (``s`` = the rank the row
+    came from). Same kernels as :func:`layer` except that the gather copies instead of quantizing."""
+    w13, sw13, w2, sw2 = experts.w13, experts.sw13, experts.w2, experts.sw2
+    r, h = int(rx_q.shape[0]), int(rx_q.shape[1])
+    if r == 0:
+        return
+    e, two_i, _ = (int(v) for v in w13.shape)
+    inter = two_i // 2
+    topk = int(topk_ids.shape[1])
+    dev = rx_q.device
+    _require_experts_aligned(w13, sw13, w2, sw2, "expert-parallel")
+    plan = _layer_plan(r, topk, e, h, inter)
+    with torch.cuda.device(dev):
+        mplan = _ops.moe_plan(r, topk, e)
+        masked_m, blk0, slot, blk_expert = _ops.moe_route(topk_ids, e, mplan)
+        region = torch.empty((plan.region,), dtype=torch.uint8, device=dev)
+        hq = region[:plan.rows * h].view(FP8).view(plan.rows, h)
+        sh = region[plan.sh_off:plan.sh_off + 4 * plan.rows * (h // 128)].view(torch.int32)
+        dq = torch.empty((plan.rows, inter), dtype=FP8, device=dev)
+        sd = torch.empty((plan.rows * (inter // 128),), dtype=torch.int32, device=dev)
+        _ops.moe_gather_rows(rx_q, rx_w, slot, topk, hq, sh)
+        _ops.moe_fc1_swiglu(hq, sh, w13, sw13, blk0, blk_expert, dq, sd)
+        dn = region[:2 * plan.rows * h].view(torch.bfloat16).view(plan.rows, h)
+        _ops.moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn)
+        _ops.moe_combine_scatter(dn, slot, topk_w, recv_off, back_base, peer_back, world)
+
+
 @torch.library.custom_op(
     "fish_scales_ops::moe_layer",
     mutates_args=(),

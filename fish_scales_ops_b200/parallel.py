@@ -103,9 +103,136 @@ def _a2a_rows_async(rows: torch.Tensor, in_counts, out_counts, group):
     return out, work
 
 
+# ------------------------------------------------------------------------------- the exchange over peer memory
+
+def _align_up(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class _PeerBuffers:
+    """Receive buffers of one rank, allocated as symmetric memory so that every rank of the group holds the
+    addresses of every other rank's copy: dispatch rows (e4m3 codes, scale words, ids, weights) for up to
+    ``world * cap_tokens`` rows and combine rows (bf16) for up to ``cap_tokens * min(k, world)`` rows. Only plain
+    peer stores touch them (no multicast object is created)."""
+
+    def __init__(self, group, world: int, cap_tokens: int, h: int, k: int, device):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+
+        self.cap_tokens, self.h, self.k, self.world = cap_tokens, h, k, world
+        cap_rows = world * cap_tokens
+        cap_back = cap_tokens * min(k, world)
+        kb = h // 128
+        sizes = [("q", cap_rows * h), ("w", cap_rows * kb * 4), ("ids", cap_rows * k * 4), ("wt", cap_rows * k * 4),
+                 ("back", cap_back * h * 2)]
+        offs, total = {}, 0
+        for name, n in sizes:
+            offs[name] = total
+            total = _align_up(total + n, 256)
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        handle = symm.rendezvous(self.buf, dist.group.WORLD if group is None else group)
+        bases = [int(p) for p in handle.buffer_ptrs]
+        self._handle = handle
+
+        def table(name):
+            return torch.tensor([b + offs[name] for b in bases], dtype=torch.int64, device=device)
+
+        def view(name, n):
+            return self.buf[offs[name]:offs[name] + n]
+
+        self.peer_q, self.peer_w, self.peer_ids = table("q"), table("w"), table("ids")
+        self.peer_wt, self.peer_back = table("wt"), table("back")
+        self.rx_q = view("q", cap_rows * h).view(torch.float8_e4m3fn).view(cap_rows, h)
+        self.rx_w = view("w", cap_rows * kb * 4).view(torch.int32).view(cap_rows, kb)
+        self.rx_ids = view("ids", cap_rows * k * 4).view(torch.int32).view(cap_rows, k)
+        self.rx_wt = view("wt", cap_rows * k * 4).view(torch.float32).view(cap_rows, k)
+        self.rx_back = view("back", cap_back * h * 2).view(torch.bfloat16).view(cap_back, h)
+        self.fence_word = torch.zeros((1,), dtype=torch.float32, device=device)
+
+
+_PEER_BUFFERS = {}
+_RETIRED_BUFFERS = []     # outgrown buffers stay mapped: a peer may still have stores to them in flight
+
+
+def _peer_buffers(group, world: int, tokens_max: int, h: int, k: int, device) -> _PeerBuffers:
+    """The buffers for this (group, H, k), grown (by at least 2x) when a batch needs more rows than they hold.
+    ``tokens_max`` is the largest token count over the ranks, which every rank knows, so that every rank takes the
+    same decision and the collective allocation matches."""
+    key = (id(group) if group is not None else 0, h, k, str(device))
+    have = _PEER_BUFFERS.get(key)
+    if have is not None and have.cap_tokens >= tokens_max:
+        return have
+    cap = _align_up(max(tokens_max, 1), 1024)
+    if have is not None:
+        cap = max(cap, 2 * have.cap_tokens)
+        _RETIRED_BUFFERS.append(have)
+    _PEER_BUFFERS[key] = _PeerBuffers(group, world, cap, h, k, device)
+    return _PEER_BUFFERS[key]
+
+
+def _fence(bufs: _PeerBuffers, group) -> None:
+    """Orders the ranks on their streams: the collective completes on a rank only after every rank's stream has
+    reached it, that is after every rank's earlier kernels (and their peer stores) have completed."""
+    dist.all_reduce(bufs.fence_word, group=group)
+
+
+def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: int, group) -> torch.Tensor:
+    """Expert parallelism with the rows stored straight into the destination GPU's memory.
+
+    1. every rank quantizes its tokens once (codes + scale words; half the bytes of the bf16 rows on the wire),
+       counts its rows per destination, and one all-gather of the counts gives every rank the full world x world
+       table (the only host read); all offsets follow from the table on the device;
+    2. the dispatch kernel stores each sent row (codes, scale words, local ids, weights) into the destination's
+       receive buffers;
+    3. after a fence the local layer runs over the received rows (its gather copies the codes instead of quantizing)
+       and its combine kernel stores each partial row into the source rank's receive buffer, at the position the row
+       had in the source's send order;
+    4. after a second fence the source adds a token's partial rows in rank order (fp32, one rounding)."""
+    from . import _ops, moe
+
+    rank = dist.get_rank(group)
+    t, h, k = int(hidden.shape[0]), int(hidden.shape[1]), int(topk_ids.shape[1])
+    dev = hidden.device
+    ids32 = topk_ids.to(torch.int32).contiguous()
+    w32 = topk_w.to(torch.float32).contiguous()
+    ids = ids32.to(torch.int64)
+    owner = torch.where((ids >= 0) & (ids < per * world), ids // per, torch.full_like(ids, world))
+    needs_t = torch.zeros((t, world + 1), dtype=torch.bool, device=dev).scatter_(1, owner, True)[:, :world] \
+        .t().contiguous()                                                    # [G, T]
+    row = torch.cat([needs_t.sum(dim=1), torch.full((1,), t, dtype=torch.int64, device=dev)])
+    table = torch.empty((world, world + 1), dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(table, row, group=group)
+    host = table.tolist()                                                     # the one host read
+    send_total = sum(host[rank][:world])
+    recv_total = sum(host[s][rank] for s in range(world))
+    bufs = _peer_buffers(group, world, max(r[world] for r in host), h, k, dev)
+
+    cm = table[:, :world]
+    send_off = torch.cumsum(cm[rank], 0) - cm[rank]                           # start of each destination's group
+    dst_base = cm[:rank].sum(dim=0)                                           # rows lower ranks put there first
+    recv_off = torch.cat([torch.zeros((1,), dtype=torch.int64, device=dev), torch.cumsum(cm[:, rank], 0)])
+    back_base = (torch.cumsum(cm, 1) - cm)[:, rank].contiguous()              # my group's start in each source's order
+    pairs = torch.nonzero_static(needs_t, size=send_total)                    # (rank, token), rank-major
+    send_rank, send_token = pairs[:, 0].contiguous(), pairs[:, 1].contiguous()
+
+    if t > 0:
+        xq, xs = _ops.quantize_1x32_fp8(hidden)
+        _ops.ep_dispatch_push(xq, xs, ids32, w32, send_token, send_rank, send_off, dst_base, bufs.peer_q, bufs.peer_w,
+                              bufs.peer_ids, bufs.peer_wt, per)
+    _fence(bufs, group)
+    moe._run_layer_rows(bufs.rx_q[:recv_total], bufs.rx_w[:recv_total], experts, bufs.rx_ids[:recv_total],
+                        bufs.rx_wt[:recv_total], recv_off, back_base, bufs.peer_back, world)
+    _fence(bufs, group)
+    pos = (torch.cumsum(needs_t.reshape(-1), 0, dtype=torch.int32) - 1).view(world, t)
+    slot = torch.where(needs_t, pos, torch.full_like(pos, -1)).t().contiguous()
+    ones = torch.ones((t, world), dtype=torch.float32, device=dev)
+    return _combine_partials(bufs.rx_back[:send_total], slot, ones)
+
+
 def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *,
                           num_experts_global: int, group=None, layer_fn: Optional[Callable] = None,
-                          combine_fn: Optional[Callable] = None, micro_batches: Optional[int] = None) -> torch.Tensor:
+                          combine_fn: Optional[Callable] = None, micro_batches: Optional[int] = None,
+                          transport: Optional[str] = None) -> torch.Tensor:
     """One MoE layer under expert parallelism: ``hidden`` bf16 ``[T, H]`` are this rank's tokens, ``topk_ids``
     ``[T, k]`` are GLOBAL expert ids, ``experts`` holds this rank's local experts. Returns the full result
     ``[T, H]`` for this rank's tokens (bf16), equal to the single-GPU layer over all experts up to the rounding of
@@ -116,9 +243,30 @@ def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor,
     issued asynchronously: while the grouped GEMMs of one slice run, the next slice's dispatch and the previous
     slice's combine are on the wire.
 
+    ``transport``: ``"peer"`` stores the rows straight into the destination GPU's memory with this library's
+    kernels (:func:`_expert_parallel_peer`); ``"collective"`` moves them with ``all_to_all_single``. The default is
+    ``"peer"`` for CUDA tensors when neither stand-in function nor micro-batching is asked for (the environment
+    variable ``FSO_B200_EP_TRANSPORT`` overrides the default); both give the same bytes.
+
     ``layer_fn(hidden, experts, local_ids, weights)`` defaults to :func:`fish_scales_ops_b200.moe.layer` and
     ``combine_fn(back, slot, ones)`` to the library's combine kernel; the CPU tests of the exchange logic pass
     stand-ins for both."""
+    if transport is None:
+        transport = os.environ.get("FSO_B200_EP_TRANSPORT", "")
+        if transport == "":
+            sliced = micro_batches not in (None, 1) or os.environ.get("FSO_B200_EP_MICRO_BATCHES", "") not in ("", "1")
+            transport = ("peer" if hidden.is_cuda and layer_fn is None and combine_fn is None and not sliced
+                         else "collective")
+    if transport not in ("peer", "collective"):
+        raise ValueError(f"expert_parallel_layer: transport {transport!r}; the transports are 'peer' and 'collective'")
+    if transport == "peer":
+        if layer_fn is not None or combine_fn is not None or micro_batches not in (None, 1):
+            raise ValueError("expert_parallel_layer: transport 'peer' runs the library's own layer in one slice; "
+                             "stand-in functions and micro-batching need transport 'collective'")
+        world = dist.get_world_size(group)
+        if num_experts_global % world != 0:
+            raise ValueError(f"expert_parallel_layer: {num_experts_global} experts over {world} ranks")
+        return _expert_parallel_peer(hidden, experts, topk_ids, topk_w, num_experts_global // world, world, group)
     if layer_fn is None:
         from . import moe
 

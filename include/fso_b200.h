@@ -119,6 +119,35 @@ int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2,
 int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,
                     const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, void* stream);
 
+/* ---- Expert-parallel exchange over peer memory -------------------------------------------------------------------
+ * The reference has no communication code: docs/guide.md:139-141 and python/fish_scales_ops/moe/__init__.py:733-739
+ * leave sharding and the exchange to the caller. The three entry points below have no counterpart there; they serve
+ * this library's expert_parallel_layer helper. They never wait on another GPU: a kernel only stores into peer-mapped
+ * buffers, and the caller orders the ranks with a stream-ordered collective before anything reads those buffers. */
+
+/* Dispatch: sent row i is token send_token[i] for rank send_rank[i] (rows grouped by rank, group r starting at
+ * send_off[r]); it is stored at row dst_base[r] + (i - send_off[r]) of rank r's receive buffers, whose addresses are
+ * peer_q[r] (e4m3 [*, H]), peer_w[r] (uint32 scale words [*, H/128], row-major), peer_ids[r] (int32 [*, topk], ids
+ * rewritten to r's local expert range, -1 elsewhere) and peer_wt[r] (fp32 [*, topk]). xq / xs are this rank's
+ * tokens as fso_quantize_1x32 wrote them. All index arrays are device memory. */
+int fso_ep_dispatch_push(const void* xq, const void* xs, const int32_t* topk_ids, const float* topk_w,
+                         const int64_t* send_token, const int64_t* send_rank, const int64_t* send_off,
+                         const int64_t* dst_base, const uint64_t* peer_q, const uint64_t* peer_w,
+                         const uint64_t* peer_ids, const uint64_t* peer_wt, int64_t rows, int64_t topk, int64_t h,
+                         int64_t experts_per_rank, void* stream);
+
+/* Received rows (codes [rows_in, H] and scale words [rows_in, H/128], both row-major) -> the compact slot order:
+ * the same outputs as fso_moe_gather_quant for rows that were quantized by their sender. */
+int fso_moe_gather_rows(const void* rx_q, const void* rx_w, const int32_t* slot_of_flat, int64_t rows_in,
+                        int64_t topk, int64_t h, int64_t rows, void* hq, void* sh, void* stream);
+
+/* fso_moe_combine without bias whose output row t goes to row back_base[s] + (t - recv_off[s]) of the bf16 [*, H]
+ * buffer at address peer_back[s], s being the source rank with recv_off[s] <= t < recv_off[s + 1] (recv_off has
+ * world + 1 entries). top-k <= 8, H a multiple of 64, dn 32-byte aligned. */
+int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const float* topk_w, int64_t tokens,
+                            int64_t topk, int64_t h, const int64_t* recv_off, const int64_t* back_base,
+                            const uint64_t* peer_back, int64_t world, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

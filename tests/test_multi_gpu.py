@@ -1,6 +1,7 @@
 """The two ways the path shards, on two GPUs of one box (skipped with fewer): the column-parallel N-split of a dense
-linear (no collective) and the expert-parallel MoE layer with NCCL all-to-all-v dispatch and combine. Each rank is
-a child process; NVLS is switched off for NCCL in them."""
+linear (no collective) and the expert-parallel MoE layer, once with the rows stored into the peer GPU's memory by the
+library's kernels and once with NCCL all-to-all-v dispatch and combine. Each rank is a child process; NVLS is
+switched off for NCCL in them and no multicast object is created for the symmetric buffers."""
 import os
 import socket
 
@@ -55,9 +56,15 @@ def _worker(rank, world, port, ret):
         e0, e1 = parallel.expert_shard(E, world, rank)
         experts = fso.moe.prepare_experts(w13[e0:e1].cuda(), w2[e0:e1].cuda(), format="mxfp8")
         hidden, ids, wts = _moe_batch(rank)
-        out = parallel.expert_parallel_layer(hidden.cuda(), experts, ids.cuda(), wts.cuda(), num_experts_global=E)
+        hidden, ids, wts = hidden.cuda(), ids.cuda(), wts.cuda()
+        out = parallel.expert_parallel_layer(hidden, experts, ids, wts, num_experts_global=E, transport="peer")
+        # the receive buffers are reused: another batch in between, then the first one again
+        other = parallel.expert_parallel_layer(hidden.flip(0).contiguous(), experts, ids, wts, num_experts_global=E,
+                                               transport="peer")
+        again = parallel.expert_parallel_layer(hidden, experts, ids, wts, num_experts_global=E)
+        coll = parallel.expert_parallel_layer(hidden, experts, ids, wts, num_experts_global=E, transport="collective")
         torch.cuda.synchronize()
-        ret[rank] = (y_part.cpu(), out.cpu(), _ops.device_status())
+        ret[rank] = (y_part.cpu(), out.cpu(), _ops.device_status(), again.cpu(), coll.cpu(), other.cpu())
     finally:
         dist.destroy_process_group()
 
@@ -83,3 +90,7 @@ def test_n_split_and_expert_parallel_on_two_gpus(fso, oracle):
                                 inputs.to_np_u32(ex.sw2), ids, wts)
         inputs.assert_close_to_oracle(ret[rank][1], want, f"expert parallel rank {rank}")
         assert ret[rank][2] == 0
+        # same bytes on a second use of the buffers and through the collective transport
+        assert torch.equal(ret[rank][1].view(torch.int16), ret[rank][3].view(torch.int16))
+        assert torch.equal(ret[rank][1].view(torch.int16), ret[rank][4].view(torch.int16))
+        assert not torch.equal(ret[rank][1].view(torch.int16), ret[rank][5].view(torch.int16))
