@@ -154,6 +154,33 @@ def moe_combine(dn, slot, topk_w, bias, bias_scale, out):
                                     stream_ptr()), "fso_moe_combine")
 
 
+def ep_plan_count(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """int32 [T, k] global ids -> (rank_mask int64 [T], row int64 [world + 1] = rows per destination rank, T)."""
+    t, k = int(topk_ids.shape[0]), int(topk_ids.shape[1])
+    dev = topk_ids.device
+    with torch.cuda.device(dev):
+        mask = torch.empty((t,), dtype=torch.int64, device=dev)
+        row = torch.empty((world + 1,), dtype=torch.int64, device=dev)
+        check(lib().fso_ep_plan_count(ptr(topk_ids), t, k, int(experts_per_rank), int(world), ptr(mask), ptr(row),
+                                      stream_ptr()), "fso_ep_plan_count")
+    return mask, row
+
+
+def ep_plan_place(mask: torch.Tensor, table: torch.Tensor, world: int, rank: int, send_total: int):
+    """-> (send_token [S], send_rank [S], send_off [G], dst_base [G], recv_off [G + 1], back_base [G], slot [T, G])."""
+    t, dev = int(mask.shape[0]), mask.device
+    with torch.cuda.device(dev):
+        lists = torch.empty((2, max(send_total, 1)), dtype=torch.int64, device=dev)
+        offs = torch.empty((4 * world + 1,), dtype=torch.int64, device=dev)
+        slot = torch.empty((t, world), dtype=torch.int32, device=dev)
+        send_off, dst_base = offs[:world], offs[world:2 * world]
+        back_base, recv_off = offs[2 * world:3 * world], offs[3 * world:]
+        check(lib().fso_ep_plan_place(ptr(mask), ptr(table), t, int(world), int(rank), ptr(lists[0]), ptr(lists[1]),
+                                      ptr(send_off), ptr(dst_base), ptr(recv_off), ptr(back_base), ptr(slot),
+                                      stream_ptr()), "fso_ep_plan_place")
+    return lists[0, :send_total], lists[1, :send_total], send_off, dst_base, recv_off, back_base, slot
+
+
 def ep_dispatch_push(xq, xs, topk_ids, topk_w, send_token, send_rank, send_off, dst_base, peer_q, peer_w, peer_ids,
                      peer_wt, experts_per_rank: int):
     """Store this rank's sent rows into the destination ranks' receive buffers (peer-mapped addresses)."""

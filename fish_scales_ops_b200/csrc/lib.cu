@@ -389,6 +389,35 @@ int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const f
         h, RowScatter{recv_off, back_base, peer_back, static_cast<int>(world)}, stream);
 }
 
+int fso_ep_plan_count(const int32_t* topk_ids, int64_t tokens, int64_t topk, int64_t experts_per_rank, int64_t world,
+    uint64_t* rank_mask, int64_t* row, void* stream)
+{
+    FSO_REQUIRE(tokens >= 0 && tokens < (1ll << 31) && topk >= 1 && experts_per_rank >= 1
+            && experts_per_rank < (1ll << 31) && world >= 1 && world <= 64,
+        "fso_ep_plan_count: 1 <= world <= 64, top-k >= 1 and experts_per_rank >= 1 required");
+    FSO_REQUIRE(row && (tokens == 0 || (topk_ids && rank_mask)), "fso_ep_plan_count: NULL pointer");
+    FSO_CUDA(cudaMemsetAsync(row, 0, sizeof(int64_t) * (world + 1), as_stream(stream)));
+    unsigned const blocks = tokens == 0 ? 1u : static_cast<unsigned>((tokens + 255) / 256);
+    ep_plan_count_kernel<<<blocks, 256, 0, as_stream(stream)>>>(topk_ids, tokens, static_cast<int>(topk),
+        static_cast<int>(experts_per_rank), static_cast<int>(world), rank_mask,
+        reinterpret_cast<unsigned long long*>(row));
+    return launch_status("ep_plan_count_kernel");
+}
+
+int fso_ep_plan_place(const uint64_t* rank_mask, const int64_t* table, int64_t tokens, int64_t world, int64_t rank,
+    int64_t* send_token, int64_t* send_rank, int64_t* send_off, int64_t* dst_base, int64_t* recv_off,
+    int64_t* back_base, int32_t* slot, void* stream)
+{
+    FSO_REQUIRE(tokens >= 0 && tokens < (1ll << 31) && world >= 1 && world <= 64 && rank >= 0 && rank < world,
+        "fso_ep_plan_place: 1 <= world <= 64 and 0 <= rank < world required");
+    FSO_REQUIRE(table && send_off && dst_base && recv_off && back_base, "fso_ep_plan_place: NULL pointer");
+    FSO_REQUIRE(tokens == 0 || (rank_mask && send_token && send_rank && slot), "fso_ep_plan_place: NULL pointer");
+    ep_plan_place_kernel<<<static_cast<unsigned>(world), 1024, 0, as_stream(stream)>>>(rank_mask, table, tokens,
+        static_cast<int>(world), static_cast<int>(rank), send_token, send_rank, send_off, dst_base, recv_off, back_base,
+        slot);
+    return launch_status("ep_plan_place_kernel");
+}
+
 int fso_ep_dispatch_push(const void* xq, const void* xs, const int32_t* topk_ids, const float* topk_w,
     const int64_t* send_token, const int64_t* send_rank, const int64_t* send_off, const int64_t* dst_base,
     const uint64_t* peer_q, const uint64_t* peer_w, const uint64_t* peer_ids, const uint64_t* peer_wt, int64_t rows,

@@ -148,6 +148,7 @@ class _PeerBuffers:
         self.rx_wt = view("wt", cap_rows * k * 4).view(torch.float32).view(cap_rows, k)
         self.rx_back = view("back", cap_back * h * 2).view(torch.bfloat16).view(cap_back, h)
         self.fence_word = torch.zeros((1,), dtype=torch.float32, device=device)
+        self.ones = torch.ones((cap_tokens, world), dtype=torch.float32, device=device)
 
 
 _PEER_BUFFERS = {}
@@ -179,9 +180,10 @@ def _fence(bufs: _PeerBuffers, group) -> None:
 def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: int, group) -> torch.Tensor:
     """Expert parallelism with the rows stored straight into the destination GPU's memory.
 
-    1. every rank quantizes its tokens once (codes + scale words; half the bytes of the bf16 rows on the wire),
-       counts its rows per destination, and one all-gather of the counts gives every rank the full world x world
-       table (the only host read); all offsets follow from the table on the device;
+    1. every rank quantizes its tokens once (codes + scale words; half the bytes of the bf16 rows on the wire) and
+       counts its rows per destination (one kernel); one all-gather of the counts gives every rank the full
+       world x world table (the only host read), from which a second kernel derives every offset, the send list and
+       the slot table of step 4;
     2. the dispatch kernel stores each sent row (codes, scale words, local ids, weights) into the destination's
        receive buffers;
     3. after a fence the local layer runs over the received rows (its gather copies the codes instead of quantizing)
@@ -195,25 +197,15 @@ def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: in
     dev = hidden.device
     ids32 = topk_ids.to(torch.int32).contiguous()
     w32 = topk_w.to(torch.float32).contiguous()
-    ids = ids32.to(torch.int64)
-    owner = torch.where((ids >= 0) & (ids < per * world), ids // per, torch.full_like(ids, world))
-    needs_t = torch.zeros((t, world + 1), dtype=torch.bool, device=dev).scatter_(1, owner, True)[:, :world] \
-        .t().contiguous()                                                    # [G, T]
-    row = torch.cat([needs_t.sum(dim=1), torch.full((1,), t, dtype=torch.int64, device=dev)])
+    mask, row = _ops.ep_plan_count(ids32, per, world)
     table = torch.empty((world, world + 1), dtype=torch.int64, device=dev)
     dist.all_gather_into_tensor(table, row, group=group)
     host = table.tolist()                                                     # the one host read
     send_total = sum(host[rank][:world])
     recv_total = sum(host[s][rank] for s in range(world))
     bufs = _peer_buffers(group, world, max(r[world] for r in host), h, k, dev)
-
-    cm = table[:, :world]
-    send_off = torch.cumsum(cm[rank], 0) - cm[rank]                           # start of each destination's group
-    dst_base = cm[:rank].sum(dim=0)                                           # rows lower ranks put there first
-    recv_off = torch.cat([torch.zeros((1,), dtype=torch.int64, device=dev), torch.cumsum(cm[:, rank], 0)])
-    back_base = (torch.cumsum(cm, 1) - cm)[:, rank].contiguous()              # my group's start in each source's order
-    pairs = torch.nonzero_static(needs_t, size=send_total)                    # (rank, token), rank-major
-    send_rank, send_token = pairs[:, 0].contiguous(), pairs[:, 1].contiguous()
+    send_token, send_rank, send_off, dst_base, recv_off, back_base, slot = _ops.ep_plan_place(
+        mask, table, world, rank, send_total)
 
     if t > 0:
         xq, xs = _ops.quantize_1x32_fp8(hidden)
@@ -223,10 +215,7 @@ def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: in
     moe._run_layer_rows(bufs.rx_q[:recv_total], bufs.rx_w[:recv_total], experts, bufs.rx_ids[:recv_total],
                         bufs.rx_wt[:recv_total], recv_off, back_base, bufs.peer_back, world)
     _fence(bufs, group)
-    pos = (torch.cumsum(needs_t.reshape(-1), 0, dtype=torch.int32) - 1).view(world, t)
-    slot = torch.where(needs_t, pos, torch.full_like(pos, -1)).t().contiguous()
-    ones = torch.ones((t, world), dtype=torch.float32, device=dev)
-    return _combine_partials(bufs.rx_back[:send_total], slot, ones)
+    return _combine_partials(bufs.rx_back[:send_total], slot, bufs.ones[:t])
 
 
 def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *,

@@ -121,9 +121,23 @@ int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* to
 
 /* ---- Expert-parallel exchange over peer memory -------------------------------------------------------------------
  * The reference has no communication code: docs/guide.md:139-141 and python/fish_scales_ops/moe/__init__.py:733-739
- * leave sharding and the exchange to the caller. The three entry points below have no counterpart there; they serve
+ * leave sharding and the exchange to the caller. The entry points below have no counterpart there; they serve
  * this library's expert_parallel_layer helper. They never wait on another GPU: a kernel only stores into peer-mapped
  * buffers, and the caller orders the ranks with a stream-ordered collective before anything reads those buffers. */
+
+/* Plan, step 1: rank_mask[t] bit r = token t has a top-k id in rank r's expert range [r * experts_per_rank, (r + 1) *
+ * experts_per_rank); row[r] = number of this rank's tokens bound for rank r, row[world] = tokens. world <= 64. */
+int fso_ep_plan_count(const int32_t* topk_ids, int64_t tokens, int64_t topk, int64_t experts_per_rank, int64_t world,
+                      uint64_t* rank_mask, int64_t* row, void* stream);
+
+/* Plan, step 2, from the all-gathered rows (table[s * (world + 1) + d] = rows rank s sends to rank d): this rank's
+ * send list (send_token / send_rank, grouped by destination, tokens ascending; as many entries as the table says this
+ * rank sends), send_off [world], dst_base [world], recv_off [world + 1], back_base [world] as the other entry points
+ * take them, and slot int32 [tokens, world] = position of (token, rank) in the send list or -1, which is the slot
+ * table of the final fso_moe_combine over the returned partial rows. */
+int fso_ep_plan_place(const uint64_t* rank_mask, const int64_t* table, int64_t tokens, int64_t world, int64_t rank,
+                      int64_t* send_token, int64_t* send_rank, int64_t* send_off, int64_t* dst_base, int64_t* recv_off,
+                      int64_t* back_base, int32_t* slot, void* stream);
 
 /* Dispatch: sent row i is token send_token[i] for rank send_rank[i] (rows grouped by rank, group r starting at
  * send_off[r]); it is stored at row dst_base[r] + (i - send_off[r]) of rank r's receive buffers, whose addresses are
