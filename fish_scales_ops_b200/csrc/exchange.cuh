@@ -2,7 +2,8 @@
 // buffers (plain st.global on peer-mapped addresses, NVLink through NVSwitch) and that unpack what arrived.
 //
 // Nothing here waits on another GPU. A kernel only writes peer memory; the ranks order their steps on the host side
-// with a stream-ordered collective between the writing kernel and the first kernel that reads what was written.
+// with a stream-ordered collective between the writing kernel and the first kernel that reads what was written
+// (a kernel's peer stores are complete when the kernel is, so the kernels issue no system-scope fence themselves).
 // The reference has no communication code (docs/guide.md:139-141 leaves sharding to the caller), so these kernels
 // serve this library's own expert_parallel_layer helper.
 #pragma once
@@ -112,9 +113,11 @@ __global__ void __launch_bounds__(128) ep_push_rows_kernel(const uint4* __restri
     const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_w, const int64_t* __restrict__ send_token,
     const int64_t* __restrict__ send_rank, const int64_t* __restrict__ send_off, const int64_t* __restrict__ dst_base,
     const uint64_t* __restrict__ peer_q, const uint64_t* __restrict__ peer_w, const uint64_t* __restrict__ peer_ids,
-    const uint64_t* __restrict__ peer_wt, int topk, int kb, int experts_per_rank)
+    const uint64_t* __restrict__ peer_wt, int topk, int kb, int experts_per_rank, int64_t rows, int64_t row_mul)
 {
-    int64_t const i = blockIdx.x;
+    // CTA b takes row (b * row_mul) mod rows, row_mul coprime to rows: the rows in flight at any moment are spread
+    // over all destinations, instead of every rank storing into the same GPU at the same time
+    int64_t const i = static_cast<int64_t>((static_cast<unsigned long long>(blockIdx.x) * row_mul) % rows);
     int64_t const tok = __ldg(send_token + i);
     int const rk = static_cast<int>(__ldg(send_rank + i));
     int64_t const row = __ldg(dst_base + rk) + (i - __ldg(send_off + rk));
@@ -131,7 +134,6 @@ __global__ void __launch_bounds__(128) ep_push_rows_kernel(const uint4* __restri
             = (id >= lo && id < lo + experts_per_rank) ? id - lo : -1;
         reinterpret_cast<float*>(__ldg(peer_wt + rk))[row * topk + threadIdx.x] = __ldg(topk_w + tok * topk + threadIdx.x);
     }
-    __threadfence_system();
 }
 
 // Received rows (codes row-major, scale words row-major) -> the compact slot order the grouped GEMM reads: codes to

@@ -327,6 +327,14 @@ int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2,
         as_stream(stream));
 }
 
+// A multiplier coprime to n (a prime that does not divide it): v -> (v * mul) mod n is then a permutation of [0, n).
+static int64_t coprime_multiplier(int64_t n)
+{
+    for (int64_t p : {1000003ll, 999983ll, 7919ll, 104729ll})
+        if (n % p != 0) return p;
+    return 1;
+}
+
 static int launch_combine(const char* op, const void* dn, const int32_t* slot_of_flat, const float* topk_w,
     const void* bias, const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, RowScatter sc,
     void* stream)
@@ -372,7 +380,7 @@ int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* to
         "fso_moe_combine: dn, out and bias must be 16-byte aligned");
     FSO_REQUIRE(bias != nullptr || bias_scale == nullptr, "fso_moe_combine: bias_scale scales bias and needs it");
     return launch_combine("fso_moe_combine", dn, slot_of_flat, topk_w, bias, bias_scale, out, tokens, topk, h,
-        RowScatter{nullptr, nullptr, nullptr, 0}, stream);
+        RowScatter{nullptr, nullptr, nullptr, 0, 1}, stream);
 }
 
 int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const float* topk_w, int64_t tokens,
@@ -386,7 +394,7 @@ int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const f
         "fso_moe_combine_scatter: NULL pointer");
     FSO_REQUIRE((reinterpret_cast<uintptr_t>(dn) & 31u) == 0, "fso_moe_combine_scatter: dn must be 32-byte aligned");
     return launch_combine("fso_moe_combine_scatter", dn, slot_of_flat, topk_w, nullptr, nullptr, nullptr, tokens, topk,
-        h, RowScatter{recv_off, back_base, peer_back, static_cast<int>(world)}, stream);
+        h, RowScatter{recv_off, back_base, peer_back, static_cast<int>(world), coprime_multiplier(tokens)}, stream);
 }
 
 int fso_ep_plan_count(const int32_t* topk_ids, int64_t tokens, int64_t topk, int64_t experts_per_rank, int64_t world,
@@ -432,7 +440,8 @@ int fso_ep_dispatch_push(const void* xq, const void* xs, const int32_t* topk_ids
     FSO_REQUIRE(aligned16(xq), "fso_ep_dispatch_push: xq must be 16-byte aligned");
     ep_push_rows_kernel<<<static_cast<unsigned>(rows), 128, 0, as_stream(stream)>>>(static_cast<const uint4*>(xq),
         static_cast<const uint32_t*>(xs), topk_ids, topk_w, send_token, send_rank, send_off, dst_base, peer_q, peer_w,
-        peer_ids, peer_wt, static_cast<int>(topk), static_cast<int>(h / 128), static_cast<int>(experts_per_rank));
+        peer_ids, peer_wt, static_cast<int>(topk), static_cast<int>(h / 128), static_cast<int>(experts_per_rank), rows,
+        coprime_multiplier(rows));
     return launch_status("ep_push_rows_kernel");
 }
 

@@ -295,11 +295,16 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
 // Where the combine's output rows go when they are not one dense [tokens, H] tensor: token t, which lies in
 // [recv_off[s], recv_off[s + 1]) for exactly one s < world, is written to row back_base[s] + (t - recv_off[s]) of the
 // bf16 [*, H] buffer at address peer_back[s] (another GPU's memory under expert parallelism). world == 0: dense.
+// Tokens are then visited in the order (v * row_mul) mod tokens (row_mul coprime to tokens) so that the rows in flight
+// at any moment are spread over all destinations. The kernel issues no system-scope fence of its own (one per CTA
+// cost 0.3 ms per layer, the CTA stays resident until every peer store is acknowledged): its stores are complete
+// when the kernel is, and the next rank reads them only after a stream-ordered collective that follows the kernel.
 struct RowScatter {
     const int64_t* recv_off;
     const int64_t* back_base;
     const uint64_t* peer_back;
     int world;
+    int64_t row_mul;
 };
 
 // The combine with 256-bit accesses: one thread owns kGroups x 16 columns of one token, so that about eight 32-byte
@@ -317,7 +322,9 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const uint8_t* __rest
     if (idx >= static_cast<uint32_t>(tokens) * per_row) return;
     uint32_t const t32 = idx / per_row;
     size_t const col = static_cast<size_t>(idx - t32 * per_row) * kSpan;
-    int64_t const t = t32;
+    int64_t const t = sc.world > 0
+        ? static_cast<int64_t>((static_cast<unsigned long long>(t32) * sc.row_mul) % static_cast<unsigned long long>(tokens))
+        : static_cast<int64_t>(t32);
     float acc[16 * kGroups];
 #pragma unroll
     for (int i = 0; i < 16 * kGroups; ++i) acc[i] = 0.f;
@@ -371,7 +378,6 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const uint8_t* __rest
                      "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
                      : "memory");
     }
-    if (sc.world > 0) __threadfence_system();
 }
 
 }  // namespace fso
