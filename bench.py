@@ -11,7 +11,8 @@ Workloads (``--workload``):
             GPU) the weight rows are split N ways (column parallel, no data-path collective); ``value`` is the whole
             job's 2*M*N*K over the slowest rank's device time.
   moe       one DeepSeek-V3-shaped MoE layer (256 experts, top-8, H=7168, I=2048), 4096 tokens per GPU, experts
-            sharded 256/N per GPU with NCCL all-to-all-v dispatch and combine (weak scaling); ``--moe-config mixtral``
+            sharded 256/N per GPU, token rows exchanged by the library's kernels over peer memory (weak scaling;
+            ``FSO_B200_EP_TRANSPORT=collective`` uses NCCL all-to-all-v instead); ``--moe-config mixtral``
             runs the 8-expert top-2 H=4096 I=14336 layer on one GPU. Metric: tokens/s.
   decode    dense linears at M=16 over the four Llama-3-8B shapes, CUDA-graph replay over rotated weight copies
             (cold weights). Metric: achieved weight-stream GB/s (worst of the four shapes).
@@ -432,6 +433,8 @@ def moe_ours(args):
         return None
     ms_step = ms_total / args.steps
     total_tokens = tokens * d.world
+    ep_transport = {"": "peer-memory stores", "peer": "peer-memory stores", "collective": "all-to-all-v"}.get(
+        os.environ.get("FSO_B200_EP_TRANSPORT", ""), "peer-memory stores")
     pairs = total_tokens * cfg["k"]
     flops = 6.0 * pairs * cfg["H"] * cfg["I"]
     pk = peaks()
@@ -443,7 +446,7 @@ def moe_ours(args):
                      "fp8_e4m3",
                      {"workload": f"{args.moe_config} MoE layer, {tokens} tokens per GPU, uniform softmax top-k routing",
                       **{k_: cfg[k_] for k_ in ("E", "k", "H", "I")},
-                      "parallelism": f"expert parallel x{d.world} (all-to-all-v dispatch + combine)" if d.world > 1
+                      "parallelism": f"expert parallel x{d.world} ({ep_transport} dispatch + combine)" if d.world > 1
                       else "single GPU", "l2": "expert weights of a step exceed L2"})
     line["roofline"] = {
         "bound": "hbm" if t_mem > t_cmp else "tensor", "kernel": "whole layer (route, gather, FC1, FC2, combine)",
@@ -454,7 +457,14 @@ def moe_ours(args):
     line["e2e"] = {"value": total_tokens / (e2e_ms / e_steps * 1e-3), "unit": "tokens/s",
                    "h2d_bytes_per_step": tokens * cfg["H"] * 2, "d2h_bytes_per_step": tokens * cfg["H"] * 2,
                    "ms_per_step": e2e_ms / e_steps}
-    line["gpu_launches"] = (7 if tokens * cfg["k"] > 1024 else 5) * args.steps
+    # own kernels per step: route (3, or 1 for small batches), gather, FC1, FC2, combine; under expert parallelism
+    # also the two plan kernels, the quantizer, the dispatch kernel and the final reduction
+    per_step = 7 if tokens * cfg["k"] > 1024 else 5
+    if d.world > 1 and ep_transport.startswith("peer"):
+        per_step += 5
+    elif d.world > 1:
+        per_step += 1
+    line["gpu_launches"] = per_step * args.steps
     line["clocks"] = clocks
     line["device_status"] = status
     if not args.no_cpu_baseline and d.world == 1:

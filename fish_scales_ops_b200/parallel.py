@@ -115,24 +115,25 @@ class _PeerBuffers:
     ``world * cap_tokens`` rows and combine rows (bf16) for up to ``cap_tokens * min(k, world)`` rows. Only plain
     peer stores touch them (no multicast object is created)."""
 
-    def __init__(self, group, world: int, cap_tokens: int, h: int, k: int, device):
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm
-
+    def __init__(self, world: int, cap_tokens: int, h: int, k: int, device, group=None, emulated_bases=None,
+                 buf=None):
+        """With ``group``: a collective symmetric allocation. With ``buf`` / ``emulated_bases`` (tests): this
+        "rank"'s buffer is the given plain tensor and the ranks' base addresses are given, all on one device."""
         self.cap_tokens, self.h, self.k, self.world = cap_tokens, h, k, world
         cap_rows = world * cap_tokens
         cap_back = cap_tokens * min(k, world)
         kb = h // 128
-        sizes = [("q", cap_rows * h), ("w", cap_rows * kb * 4), ("ids", cap_rows * k * 4), ("wt", cap_rows * k * 4),
-                 ("back", cap_back * h * 2)]
-        offs, total = {}, 0
-        for name, n in sizes:
-            offs[name] = total
-            total = _align_up(total + n, 256)
-        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
-        handle = symm.rendezvous(self.buf, dist.group.WORLD if group is None else group)
-        bases = [int(p) for p in handle.buffer_ptrs]
-        self._handle = handle
+        offs, total = self.layout(world, cap_tokens, h, k)
+        if buf is None:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+
+            self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+            handle = symm.rendezvous(self.buf, dist.group.WORLD if group is None else group)
+            bases = [int(p) for p in handle.buffer_ptrs]
+            self._handle = handle
+        else:
+            self.buf, bases = buf, [int(b) for b in emulated_bases]
 
         def table(name):
             return torch.tensor([b + offs[name] for b in bases], dtype=torch.int64, device=device)
@@ -149,6 +150,19 @@ class _PeerBuffers:
         self.rx_back = view("back", cap_back * h * 2).view(torch.bfloat16).view(cap_back, h)
         self.fence_word = torch.zeros((1,), dtype=torch.float32, device=device)
         self.ones = torch.ones((cap_tokens, world), dtype=torch.float32, device=device)
+
+    @staticmethod
+    def layout(world: int, cap_tokens: int, h: int, k: int):
+        """Byte offsets of the five regions inside one rank's buffer, and the buffer's size."""
+        cap_rows = world * cap_tokens
+        cap_back = cap_tokens * min(k, world)
+        sizes = [("q", cap_rows * h), ("w", cap_rows * (h // 128) * 4), ("ids", cap_rows * k * 4),
+                 ("wt", cap_rows * k * 4), ("back", cap_back * h * 2)]
+        offs, total = {}, 0
+        for name, n in sizes:
+            offs[name] = total
+            total = _align_up(total + n, 256)
+        return offs, total
 
 
 _PEER_BUFFERS = {}
@@ -167,7 +181,7 @@ def _peer_buffers(group, world: int, tokens_max: int, h: int, k: int, device) ->
     if have is not None:
         cap = max(cap, 2 * have.cap_tokens)
         _RETIRED_BUFFERS.append(have)
-    _PEER_BUFFERS[key] = _PeerBuffers(group, world, cap, h, k, device)
+    _PEER_BUFFERS[key] = _PeerBuffers(world, cap, h, k, device, group=group)
     return _PEER_BUFFERS[key]
 
 
@@ -190,32 +204,54 @@ def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: in
        and its combine kernel stores each partial row into the source rank's receive buffer, at the position the row
        had in the source's send order;
     4. after a second fence the source adds a token's partial rows in rank order (fp32, one rounding)."""
-    from . import _ops, moe
+    from . import _ops
 
     rank = dist.get_rank(group)
     t, h, k = int(hidden.shape[0]), int(hidden.shape[1]), int(topk_ids.shape[1])
-    dev = hidden.device
     ids32 = topk_ids.to(torch.int32).contiguous()
     w32 = topk_w.to(torch.float32).contiguous()
     mask, row = _ops.ep_plan_count(ids32, per, world)
-    table = torch.empty((world, world + 1), dtype=torch.int64, device=dev)
+    table = torch.empty((world, world + 1), dtype=torch.int64, device=hidden.device)
     dist.all_gather_into_tensor(table, row, group=group)
     host = table.tolist()                                                     # the one host read
+    bufs = _peer_buffers(group, world, max(r[world] for r in host), h, k, hidden.device)
+    st = _peer_dispatch(hidden, ids32, w32, mask, table, host, rank, world, per, bufs)
+    _fence(bufs, group)
+    _peer_local(st, experts, bufs)
+    _fence(bufs, group)
+    return _peer_reduce(st, bufs)
+
+
+def _peer_dispatch(hidden, ids32, w32, mask, table, host, rank: int, world: int, per: int, bufs: _PeerBuffers) -> dict:
+    """Steps 1-2 of :func:`_expert_parallel_peer` after the count exchange: the plan's second kernel, the quantizer
+    and the dispatch kernel. ``host`` is the table as nested python lists. Returns what the later steps need."""
+    from . import _ops
+
+    t = int(hidden.shape[0])
     send_total = sum(host[rank][:world])
     recv_total = sum(host[s][rank] for s in range(world))
-    bufs = _peer_buffers(group, world, max(r[world] for r in host), h, k, dev)
     send_token, send_rank, send_off, dst_base, recv_off, back_base, slot = _ops.ep_plan_place(
         mask, table, world, rank, send_total)
-
     if t > 0:
         xq, xs = _ops.quantize_1x32_fp8(hidden)
         _ops.ep_dispatch_push(xq, xs, ids32, w32, send_token, send_rank, send_off, dst_base, bufs.peer_q, bufs.peer_w,
                               bufs.peer_ids, bufs.peer_wt, per)
-    _fence(bufs, group)
-    moe._run_layer_rows(bufs.rx_q[:recv_total], bufs.rx_w[:recv_total], experts, bufs.rx_ids[:recv_total],
-                        bufs.rx_wt[:recv_total], recv_off, back_base, bufs.peer_back, world)
-    _fence(bufs, group)
-    return _combine_partials(bufs.rx_back[:send_total], slot, bufs.ones[:t])
+    return dict(tokens=t, world=world, send_total=send_total, recv_total=recv_total, recv_off=recv_off,
+                back_base=back_base, slot=slot)
+
+
+def _peer_local(st: dict, experts, bufs: _PeerBuffers) -> None:
+    """Step 3: the local experts over the received rows; partial rows go to their source ranks' buffers."""
+    from . import moe
+
+    n = st["recv_total"]
+    moe._run_layer_rows(bufs.rx_q[:n], bufs.rx_w[:n], experts, bufs.rx_ids[:n], bufs.rx_wt[:n], st["recv_off"],
+                        st["back_base"], bufs.peer_back, st["world"])
+
+
+def _peer_reduce(st: dict, bufs: _PeerBuffers) -> torch.Tensor:
+    """Step 4: out[t] = bf16(sum over ranks, ascending, of the partial rows that came back for token t)."""
+    return _combine_partials(bufs.rx_back[:st["send_total"]], st["slot"], bufs.ones[:st["tokens"]])
 
 
 def expert_parallel_layer(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *,
