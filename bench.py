@@ -575,7 +575,7 @@ def quantize_ours(args):
     line = base_line(args, d, "quantize_1x32_gbs", "GB/s", nbytes / us / 1e3, us / 1e3, "strong", "bf16->fp8_e4m3",
                      {"workload": f"1x32 MXFP8 activation quantizer on bf16 [{m}, {k}], {copies} rotated inputs",
                       "l2": "4 x 64 MB inputs + outputs exceed L2"})
-    line["roofline"] = {"bound": "hbm", "kernel": "quantize_1x32_kernel", "achieved": nbytes / us / 1e3,
+    line["roofline"] = {"bound": "hbm", "kernel": "quantize_1x32_wide_kernel", "achieved": nbytes / us / 1e3,
                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": nbytes / us / 1e3 / pk["hbm_gbs"],
                         "traffic": None, "peak_source": f"{pk['source']} copy bandwidth"}
     line["gpu_launches"] = copies * args.steps

@@ -23,7 +23,11 @@
 
 namespace fso {
 
-enum : int { EPI_BF16 = 0, EPI_PARTIAL = 1, EPI_SWIGLU = 2 };
+// EPI_CLUSTER (swapped orientation only): split-K inside a thread-block cluster. The CTAs of a cluster take the K
+// slices of one tile; slices 1.. store their fp32 accumulators into CTA 0's shared memory (distributed shared memory),
+// CTA 0 adds them in slice order and writes bf16: the same sums as EPI_PARTIAL + splitk_reduce_kernel, in one launch
+// and without a workspace.
+enum : int { EPI_BF16 = 0, EPI_PARTIAL = 1, EPI_SWIGLU = 2, EPI_CLUSTER = 3 };
 
 struct GemmParams {
     const uint8_t* sfa;        // scale words of the operand on MMA-M
@@ -63,9 +67,12 @@ struct GemmCfg {
     static constexpr int kSfbBytes = 512 * kSfbAtoms;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - 512 /*barriers*/;
-    static constexpr int kStagesMax = kSmemBudget / kStageBytes;
-    static constexpr int kStages = kStagesMax > 12 ? 12 : kStagesMax;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+    // EPI_CLUSTER keeps room for the other slices' accumulators: [slice - 1][BN columns][128 rows] fp32
+    static constexpr int kRedSlices = EPI != 3 /* EPI_CLUSTER */ ? 0 : BN <= 16 ? 7 : BN <= 32 ? 6 : 2;
+    static constexpr int kRedBytes = kRedSlices * BN * 512;
+    static constexpr int kStagesMax = (kSmemBudget - kRedBytes) / kStageBytes;
+    static constexpr int kStages = EPI == 3 ? (kStagesMax > 6 ? 6 : kStagesMax) : kStagesMax > 12 ? 12 : kStagesMax;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kRedBytes;
     // tensor-memory columns: accumulators first, then two alternating scale-factor buffers
     static constexpr int kAccCols = kAccStages * BN;
     static constexpr int kSfaCols = 4;
@@ -88,13 +95,14 @@ struct TileCoord {
 
 // Static schedule: work item t of (tiles_a_used * tiles_b * splits). A tiles advance fastest inside a group of
 // `group_a`, then B tiles, then the next group; the split index is the slowest inside a tile pair.
-template <bool kGrouped>
+// With kClusterK the split index is the fastest (the CTAs of one cluster share a tile).
+template <bool kGrouped, bool kClusterK = false>
 __device__ __forceinline__ bool decode_tile(GemmParams const& p, int t, int tiles_a_used, TileCoord& c)
 {
     int const per_split = tiles_a_used * p.tiles_b;
     if (t >= per_split * p.splits) return false;
-    c.split = t / per_split;
-    int const r = t - c.split * per_split;
+    c.split = kClusterK ? t % p.splits : t / per_split;
+    int const r = kClusterK ? t / p.splits : t - c.split * per_split;
     int const group_span = p.group_a * p.tiles_b;
     int const g = r / group_span;
     int const first_a = g * p.group_a;
@@ -159,6 +167,12 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t const misc_off = static_cast<uint32_t>(S) * C::kStageBytes + 8u * (2 * S + 4);
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gbase + misc_off);
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(gbase + misc_off + 4);
+    uint32_t const red_off = (misc_off + 16u + 15u) & ~15u;      // EPI_CLUSTER: the other slices' accumulators
+    static_assert(EPI != EPI_CLUSTER || kSwap, "cluster split-K serves the swapped orientation");
+    // EPI_CLUSTER: this thread's accumulator row (epilogue warps), kept in registers across the cluster barrier
+    float red_v[EPI == EPI_CLUSTER ? BN : 1];
+    bool red_have = false;
+    TileCoord red_c{};
 
     int const warp = threadIdx.x >> 5;
     int const lane = threadIdx.x & 31;
@@ -185,6 +199,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     uint32_t const tmem_base = *tmem_slot;
+    // first half of the "every CTA of the cluster has started" barrier; waited for before the first remote store
+    if constexpr (EPI == EPI_CLUSTER) cluster_arrive();
 
     int tiles_a_used = p.tiles_a;
     if constexpr (kGrouped) tiles_a_used = min(p.tiles_a, p.blk0[p.num_experts]);
@@ -197,7 +213,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t phase = 0;
             TileCoord c;
             bool ok = true;
-            for (int t = blockIdx.x; ok && decode_tile<kGrouped>(p, t, tiles_a_used, c); t += gridDim.x) {
+            for (int t = blockIdx.x; ok && decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
                 int const kb0 = c.split * p.kb_per_split;
                 int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 int const a_row0 = c.a_tile * C::kBM;
@@ -243,7 +259,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t idesc = make_idesc_mxf8(BN);
             TileCoord c;
             bool ok = true;
-            for (int t = blockIdx.x; ok && decode_tile<kGrouped>(p, t, tiles_a_used, c); t += gridDim.x) {
+            for (int t = blockIdx.x; ok && decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
                 int const kb0 = c.split * p.kb_per_split;
                 int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 if (!wait_or_abort(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
@@ -297,7 +313,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         int acc = 0;
         uint32_t acc_phase = 0;
         TileCoord c;
-        for (int t = blockIdx.x; decode_tile<kGrouped>(p, t, tiles_a_used, c); t += gridDim.x) {
+        for (int t = blockIdx.x; decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
             if (!wait_or_abort(tfull_bar(acc), acc_phase, abort_flag)) {
                 if (lane == 0) record_abort(FSO_DEV_WAIT_EPILOGUE, abort_flag);
                 break;
@@ -309,7 +325,19 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int const b_row0 = c.b_tile * BN;
             bool released = false;
 
-            if constexpr (EPI == EPI_SWIGLU) {
+            if constexpr (EPI == EPI_CLUSTER) {
+                // one work item per CTA: keep the accumulator row in registers for the reduction after the loop
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(t_row + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) red_v[c0 + j] = __uint_as_float(r[j]);
+                }
+                red_have = true;
+                red_c = c;
+            } else if constexpr (EPI == EPI_SWIGLU) {
                 // 64 interleaved (gate, up) accumulator columns per warp -> 32 outputs = one 1x32 block per row.
                 // The slice is drained into registers and the accumulator handed back before the math starts.
                 static_assert(kColsPerWarp == 64, "one 1x32 output block per warp");
@@ -447,6 +475,35 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         }
         __syncwarp();
+    }
+
+    if constexpr (EPI == EPI_CLUSTER) {
+        // ------------------------------------------------------------------ split-K reduction inside the cluster
+        uint32_t const rank = cluster_ctarank();
+        int const row = (warp & 3) * 32 + lane;
+        cluster_wait();                                   // every CTA of the cluster is running
+        if (warp >= 4 && red_have && rank != 0) {
+#pragma unroll
+            for (int j = 0; j < BN; ++j)
+                st_cluster_f32(map_to_cta(base + red_off + 4u * (((rank - 1u) * BN + j) * 128u + row), 0u), red_v[j]);
+        }
+        cluster_arrive();
+        cluster_wait();                                   // the other slices' rows are in CTA 0's shared memory
+        if (warp >= 4 && red_have && rank == 0) {
+            const float* const red = reinterpret_cast<const float*>(gbase + red_off);
+            for (int s2 = 1; s2 < p.splits; ++s2)
+#pragma unroll
+                for (int j = 0; j < BN; ++j) red_v[j] += red[((s2 - 1) * BN + j) * 128 + row];
+            int const a_row = red_c.a_tile * C::kBM + row;
+            int const b_row0 = red_c.b_tile * BN;
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                int const m = b_row0 + j;
+                if (m < p.rows_b && a_row < p.rows_a)
+                    static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row]
+                        = __float2bfloat16_rn(red_v[j]);
+            }
+        }
     }
 
     // ---------------------------------------------------------------------------------------- teardown

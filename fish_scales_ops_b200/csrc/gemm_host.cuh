@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "gemm.cuh"
 #include "gemm2.cuh"
@@ -70,12 +71,19 @@ inline double wave_efficiency(int64_t items, int sms)
     return static_cast<double>(items) / static_cast<double>(rounds * sms);
 }
 
-inline void pick_splits(int64_t tiles, int kb, int sms, int min_kb, int* splits, int* kb_per)
+// Largest split count the cluster form takes for a token tile (room for the other slices' accumulators in CTA 0's
+// shared memory; 8 is the portable cluster size).
+inline int cluster_split_limit(int bn)
+{
+    return bn <= 16 ? 8 : bn <= 32 ? 7 : bn <= 64 ? 3 : 1;
+}
+
+inline void pick_splits(int64_t tiles, int kb, int sms, int min_kb, int max_s, int* splits, int* kb_per)
 {
     int best_s = 1;
     double best = wave_efficiency(tiles, sms);
     if (tiles * 2 <= sms) {
-        for (int s = 2; s <= 16; ++s) {
+        for (int s = 2; s <= max_s; ++s) {
             int const per = (kb + s - 1) / s;
             if (per < min_kb) break;
             int const real = (kb + per - 1) / per;
@@ -101,7 +109,7 @@ inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
         p.tiles_a = static_cast<int>(n / 128);
         p.tiles_b = 1;
         p.group_a = p.tiles_a;
-        pick_splits(p.tiles_a, kb, sms, 4, &p.splits, &p.kb_per_split);
+        pick_splits(p.tiles_a, kb, sms, 4, cluster_split_limit(p.bn), &p.splits, &p.kb_per_split);
     } else {
         p.swap = false;
         int const tiles_m = static_cast<int>((m + 127) / 128);
@@ -109,7 +117,7 @@ inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
         p.tiles_a = tiles_m;
         p.tiles_b = static_cast<int>((n + p.bn - 1) / p.bn);
         p.group_a = tiles_m < 16 ? tiles_m : 16;
-        pick_splits(static_cast<int64_t>(p.tiles_a) * p.tiles_b, kb, sms, 8, &p.splits, &p.kb_per_split);
+        pick_splits(static_cast<int64_t>(p.tiles_a) * p.tiles_b, kb, sms, 8, 16, &p.splits, &p.kb_per_split);
     }
     p.ws_bytes = p.splits > 1 ? static_cast<int64_t>(p.splits) * m * n * 4 : 0;
     return p;
@@ -138,6 +146,72 @@ inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmPa
     if (rc != 0) return rc;
     kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ta, tb, p);
     return launch_status("gemm_mxf8_kernel");
+}
+
+template <int BN>
+inline void cluster_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int items, int splits,
+    cudaStream_t stream)
+{
+    using C = GemmCfg<BN, EPI_CLUSTER>;
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3(static_cast<unsigned>(items), 1, 1);
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+}
+
+// How many clusters of `splits` CTAs of the cluster split-K kernel this device runs at the same time (one CTA per
+// SM, a cluster inside one GPC); asked once per device and cluster size. 0 = cannot be launched.
+template <int BN>
+inline int cluster_capacity(int splits)
+{
+    using C = GemmCfg<BN, EPI_CLUSTER>;
+    static std::atomic<int> cap[64][9];          // 0 = not asked yet, else capacity + 1
+    static std::atomic<uint64_t> done{0};
+    int const dev = current_device() & 63;
+    if (splits < 2 || splits > 8) return 0;
+    int v = cap[dev][splits].load(std::memory_order_acquire);
+    if (v == 0) {
+        auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false>;
+        int clusters = 0;
+        if (ensure_smem_attr(kernel, C::kSmemBytes, done) == 0) {
+            cudaLaunchConfig_t cfg;
+            cudaLaunchAttribute attr[1];
+            cluster_launch_config<BN>(cfg, attr, splits, splits, nullptr);
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) {
+                (void)cudaGetLastError();
+                clusters = 0;
+            }
+        }
+        v = clusters + 1;
+        cap[dev][splits].store(v, std::memory_order_release);
+    }
+    return v - 1;
+}
+
+inline int cluster_capacity_bn(int bn, int splits)
+{
+    return bn == 16 ? cluster_capacity<16>(splits) : bn == 32 ? cluster_capacity<32>(splits)
+        : bn == 64 ? cluster_capacity<64>(splits) : 0;
+}
+
+// The swapped kernel with split-K inside thread-block clusters of `splits` CTAs (one CTA per work item).
+template <int BN>
+inline int launch_gemm_cluster(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int items,
+    cudaStream_t stream)
+{
+    auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false>;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cluster_launch_config<BN>(cfg, attr, items, p.splits, stream);
+    FSO_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
+    return launch_status("gemm_mxf8_kernel (cluster split-K)");
 }
 
 // Tensor map over a scale-word buffer seen as [atoms, 128] 32-bit words (one 512-byte atom per row), box = one atom.
@@ -213,6 +287,17 @@ inline int launch_dense_pair(const void* a, const void* sfa, const void* w, cons
     return launch_status("gemm_mxf8_pair_kernel");
 }
 
+// FSO_B200_SPLITK=workspace keeps the two-launch split-K (fp32 partials + reduce kernel) for the decode shapes too;
+// both forms give the same bytes.
+inline bool splitk_through_workspace()
+{
+    static int const v = [] {
+        const char* e = getenv("FSO_B200_SPLITK");
+        return (e != nullptr && strcmp(e, "workspace") == 0) ? 1 : 0;
+    }();
+    return v != 0;
+}
+
 // D[M, N] = A[M, K] * W[N, K]^T.
 inline int launch_dense(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
     int64_t k, void* ws, int64_t ws_bytes, cudaStream_t stream)
@@ -255,9 +340,33 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
         p.rows_a = static_cast<int>(m);
         p.rows_b = static_cast<int>(n);
     }
-    int64_t const items = static_cast<int64_t>(pl.tiles_a) * pl.tiles_b * pl.splits;
+    // Decode-sized problems sum their K slices inside clusters (one launch, no workspace traffic) when all the
+    // clusters run at the same time: take the largest slice count <= the planned one whose clusters all fit.
+    int splits = pl.splits;
+    bool in_cluster = false;
+    if (pl.swap && pl.splits > 1) {
+        for (int s2 = pl.splits; s2 >= 2; --s2) {
+            int const per = (p.kb_total + s2 - 1) / s2;
+            if ((p.kb_total + per - 1) / per != s2) continue;
+            if (cluster_capacity_bn(pl.bn, s2) >= pl.tiles_a) {
+                if (s2 == pl.splits || pl.tiles_a * s2 * 2 >= sms) {
+                    splits = s2;
+                    in_cluster = true;
+                }
+                break;
+            }
+        }
+    }
+    p.splits = splits;
+    p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    int64_t const items = static_cast<int64_t>(pl.tiles_a) * pl.tiles_b * splits;
     int const grid = static_cast<int>(items < sms ? items : sms);
-    bool const partial = pl.splits > 1;
+    if (in_cluster && !splitk_through_workspace()) {
+        return pl.bn == 16 ? launch_gemm_cluster<16>(ta, tb, p, static_cast<int>(items), stream)
+            : pl.bn == 32 ? launch_gemm_cluster<32>(ta, tb, p, static_cast<int>(items), stream)
+                          : launch_gemm_cluster<64>(ta, tb, p, static_cast<int>(items), stream);
+    }
+    bool const partial = splits > 1;
 #define FSO_DENSE_CASE(BN_, SWAP_)                                                                                 \
     if (pl.bn == BN_ && pl.swap == SWAP_) {                                                                        \
         rc = partial ? launch_gemm_inst<BN_, EPI_PARTIAL, SWAP_, false>(ta, tb, p, grid, stream)                   \
@@ -277,7 +386,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     if (partial) {
         int64_t const quads = m * n / 4;
         splitk_reduce_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, stream>>>(
-            static_cast<const float4*>(ws), static_cast<uint2*>(d), quads, pl.splits);
+            static_cast<const float4*>(ws), static_cast<uint2*>(d), quads, splits);
         rc = launch_status("splitk_reduce_kernel");
     }
     return rc;

@@ -275,6 +275,24 @@ __device__ __forceinline__ void cluster_sync_all()
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// The two halves of the cluster barrier, for code that has work to do between them. Every thread of the cluster
+// must execute each half, in the same order.
+__device__ __forceinline__ void cluster_arrive()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_wait()
+{
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// fp32 store to a cluster-window shared-memory address (another CTA's shared memory).
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
 // Arrive on an mbarrier that may live in the other CTA of the pair (cluster-window address).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {

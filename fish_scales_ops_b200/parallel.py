@@ -213,16 +213,18 @@ def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: in
     mask, row = _ops.ep_plan_count(ids32, per, world)
     table = torch.empty((world, world + 1), dtype=torch.int64, device=hidden.device)
     dist.all_gather_into_tensor(table, row, group=group)
+    quantized = _ops.quantize_1x32_fp8(hidden) if t > 0 else None            # runs while the host waits below
     host = table.tolist()                                                     # the one host read
     bufs = _peer_buffers(group, world, max(r[world] for r in host), h, k, hidden.device)
-    st = _peer_dispatch(hidden, ids32, w32, mask, table, host, rank, world, per, bufs)
+    st = _peer_dispatch(hidden, ids32, w32, mask, table, host, rank, world, per, bufs, quantized)
     _fence(bufs, group)
     _peer_local(st, experts, bufs)
     _fence(bufs, group)
     return _peer_reduce(st, bufs)
 
 
-def _peer_dispatch(hidden, ids32, w32, mask, table, host, rank: int, world: int, per: int, bufs: _PeerBuffers) -> dict:
+def _peer_dispatch(hidden, ids32, w32, mask, table, host, rank: int, world: int, per: int, bufs: _PeerBuffers,
+                   quantized=None) -> dict:
     """Steps 1-2 of :func:`_expert_parallel_peer` after the count exchange: the plan's second kernel, the quantizer
     and the dispatch kernel. ``host`` is the table as nested python lists. Returns what the later steps need."""
     from . import _ops
@@ -233,7 +235,7 @@ def _peer_dispatch(hidden, ids32, w32, mask, table, host, rank: int, world: int,
     send_token, send_rank, send_off, dst_base, recv_off, back_base, slot = _ops.ep_plan_place(
         mask, table, world, rank, send_total)
     if t > 0:
-        xq, xs = _ops.quantize_1x32_fp8(hidden)
+        xq, xs = quantized if quantized is not None else _ops.quantize_1x32_fp8(hidden)
         _ops.ep_dispatch_push(xq, xs, ids32, w32, send_token, send_rank, send_off, dst_base, bufs.peer_q, bufs.peer_w,
                               bufs.peer_ids, bufs.peer_wt, per)
     return dict(tokens=t, world=world, send_total=send_total, recv_total=recv_total, recv_off=recv_off,

@@ -213,38 +213,69 @@ def test_bit_equal_to_cublas_block_scaled_gemm(fso, device_ok, m, n, k):
     assert torch.equal(y, ref)
 
 
-def test_cta_pair_kernel_in_child_process(fso, device_ok):
-    """The opt-in CTA-pair kernel (FSO_B200_PAIR=1, read once per process, hence a child process) gives the bytes of
-    the single-CTA kernel, including a ragged M whose second CTA of the last pair has no rows."""
-    import os
-    import subprocess
-    import sys
-
-    code = r"""
+_CHILD = r"""
 import sys, torch
 sys.path.insert(0, %r); sys.path.insert(0, %r)
 import inputs
 import fish_scales_ops_b200 as fso
 from fish_scales_ops_b200 import _ops
-for m, n, k in ((2048, 4096, 512), (1920, 5120, 256), (2100, 4096, 1024)):
+for m, n, k in %r:
     x = inputs.activation(m, k, m + k).cuda()
     w = fso.dense.prepare_weight(inputs.weight(n, k, n + k).cuda(), format="mxfp8")
-    torch.save(fso.dense.linear(x, w).cpu(), sys.argv[1] + f".{m}.pt")
+    torch.save(fso.dense.linear(x, w).cpu(), sys.argv[1] + f".{m}.{n}.{k}.pt")
 assert _ops.device_status() == 0
 print("ok")
 """
+
+
+def _outputs_in_child_process(shapes, env_extra, tag):
+    """fso.dense.linear over `shapes` in a child process with extra environment (the switches are read once per
+    process)."""
+    import os
+    import subprocess
+    import sys
+
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     tmp = os.path.join(root, "gpurun_out")
     os.makedirs(tmp, exist_ok=True)
+    base = os.path.join(tmp, tag)
+    res = subprocess.run([sys.executable, "-c", _CHILD % (root, os.path.join(root, "tests"), tuple(shapes)), base],
+                         env=dict(os.environ, **env_extra), capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
     outs = {}
-    for pair in ("1", "0"):
-        env = dict(os.environ, FSO_B200_PAIR=pair)
-        base = os.path.join(tmp, f"pair{pair}")
-        res = subprocess.run([sys.executable, "-c", code % (root, os.path.join(root, "tests")), base], env=env,
-                             capture_output=True, text=True, timeout=600)
-        assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
-        outs[pair] = {m: torch.load(f"{base}.{m}.pt") for m in (2048, 1920, 2100)}
-        for m in (2048, 1920, 2100):
-            os.remove(f"{base}.{m}.pt")
-    for m in (2048, 1920, 2100):
-        assert torch.equal(outs["1"][m], outs["0"][m]), m
+    for m, n, k in shapes:
+        path = f"{base}.{m}.{n}.{k}.pt"
+        outs[(m, n, k)] = torch.load(path)
+        os.remove(path)
+    return outs
+
+
+def test_cta_pair_kernel_in_child_process(fso, device_ok):
+    """The opt-in CTA-pair kernel (FSO_B200_PAIR=1) gives the bytes of the single-CTA kernel, including a ragged M
+    whose second CTA of the last pair has no rows."""
+    shapes = ((2048, 4096, 512), (1920, 5120, 256), (2100, 4096, 1024))
+    pair = _outputs_in_child_process(shapes, {"FSO_B200_PAIR": "1"}, "pair1")
+    single = _outputs_in_child_process(shapes, {"FSO_B200_PAIR": "0"}, "pair0")
+    for shape in shapes:
+        assert torch.equal(pair[shape], single[shape]), shape
+
+
+def test_cluster_split_k_equals_workspace_split_k(fso, oracle, device_ok):
+    """Decode-sized problems sum their K slices inside thread-block clusters (one launch); FSO_B200_SPLITK=workspace
+    keeps fp32 partials in a workspace and a second kernel. Same slices, same order of additions: same bytes. The
+    shapes cover 16/32/64-wide token tiles, clusters of 2 to 8 CTAs and ragged token counts."""
+    from fish_scales_ops_b200 import _ops
+
+    shapes = ((16, 4096, 4096), (16, 6144, 4096), (5, 4096, 14336), (16, 512, 4096), (7, 384, 1024),
+              (32, 1024, 1024), (29, 2560, 2048), (64, 512, 1536), (50, 1024, 1536))
+    for m, n, k in shapes:
+        assert _ops.gemm_ws_bytes(m, n, k) > 0, "pick shapes that take the split-K route"
+    cluster = _outputs_in_child_process(shapes, {"FSO_B200_SPLITK": "cluster"}, "splitk_cluster")
+    workspace = _outputs_in_child_process(shapes, {"FSO_B200_SPLITK": "workspace"}, "splitk_ws")
+    for shape in shapes:
+        assert torch.equal(cluster[shape], workspace[shape]), shape
+    m, n, k = shapes[0]
+    x, w = inputs.activation(m, k, m + k), inputs.weight(n, k, n + k)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    ref = _oracle_out(oracle, x, inputs.to_np_u8(weight.weight), inputs.to_np_u32(weight.scale))
+    inputs.assert_close_to_oracle(cluster[shapes[0]], ref, "cluster split-K vs oracle")
