@@ -25,8 +25,9 @@ def sf_words(rows: int, k: int) -> int:
     return _align(rows, 128) * (k // 128)
 
 
-def quantize_1x32_fp8(x: torch.Tensor, interleave_i: int = 0):
-    """bf16 [M, K] -> (float8_e4m3fn [M, K], int32 [align(M,128) * K/128]); python/fish_scales_ops/gemm/mxfp8.py:191-213."""
+def quantize_1x32_fp8(x: torch.Tensor, interleave_i: int = 0, activation: bool = False):
+    """bf16 [M, K] -> (float8_e4m3fn [M, K], int32 [align(M,128) * K/128]); python/fish_scales_ops/gemm/mxfp8.py:191-213.
+    ``activation``: the form whose kernel lets a decode GEMM behind it start loading weights early (same bytes)."""
     if x.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
         raise ValueError(f"quantize_1x32_fp8: x must be a CUDA bf16 [M, K] tensor, got {x.dtype} {tuple(x.shape)}")
     x = x.contiguous()
@@ -36,10 +37,19 @@ def quantize_1x32_fp8(x: torch.Tensor, interleave_i: int = 0):
     with torch.cuda.device(x.device):
         xq = torch.empty((m, k), dtype=FP8, device=x.device)
         sf = torch.empty((sf_words(m, k),), dtype=torch.int32, device=x.device)
-        if m > 0:
+        if m > 0 and activation and interleave_i == 0:
+            check(lib().fso_quantize_activation_1x32(ptr(x), ptr(xq), ptr(sf), m, k, stream_ptr()),
+                  "fso_quantize_activation_1x32")
+        elif m > 0:
             check(lib().fso_quantize_1x32(ptr(x), ptr(xq), ptr(sf), m, k, int(interleave_i), stream_ptr()),
                   "fso_quantize_1x32")
     return xq, sf
+
+
+def stream_fence(device) -> None:
+    """One empty plain launch on the current stream of ``device`` (orders programmatic dependent launches)."""
+    with torch.cuda.device(device):
+        check(lib().fso_stream_fence(stream_ptr()), "fso_stream_fence")
 
 
 def quantize_experts_1x32_fp8(w: torch.Tensor, interleave: bool):

@@ -201,6 +201,10 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t const tmem_base = *tmem_slot;
     // first half of the "every CTA of the cluster has started" barrier; waited for before the first remote store
     if constexpr (EPI == EPI_CLUSTER) cluster_arrive();
+    // Decode-sized calls are chained with programmatic dependent launch: the next kernel may start its set-up and its
+    // weight loads while this one runs, and this one has done the same under its predecessor. Before its
+    // griddep_wait() a kernel reads only weights (immutable) and writes nothing outside its own CTA.
+    if constexpr (kSwap) griddep_launch_dependents();
 
     int tiles_a_used = p.tiles_a;
     if constexpr (kGrouped) tiles_a_used = min(p.tiles_a, p.blk0[p.num_experts]);
@@ -213,8 +217,9 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t phase = 0;
             TileCoord c;
             bool ok = true;
+            bool first_tile = true;
             for (int t = blockIdx.x; ok && decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
-                int const kb0 = c.split * p.kb_per_split;
+                int kb0 = c.split * p.kb_per_split;
                 int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 int const a_row0 = c.a_tile * C::kBM;
                 int const b_row0 = c.b_tile * BN;
@@ -225,6 +230,34 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 for (int j = 0; j < C::kSfbAtoms; ++j)
                     if (b_row0 + j * 128 < rows_b_pad) ++sfb_atoms;
                 uint32_t const bytes = C::kABytes + C::kBBytes + C::kSfaBytes + 512u * sfb_atoms;
+                if constexpr (kSwap) {
+                    if (first_tile) {
+                        // The weight side (MMA-M operand and its scales) of the first stages goes out before the
+                        // wait for the preceding kernel; the activation side, which that kernel may still be
+                        // writing, after it. All stages are free at this point, no empty-barrier wait is needed.
+                        first_tile = false;
+                        int const npre = min(S, kb1 - kb0);
+                        for (int i = 0; i < npre; ++i) {
+                            uint32_t const fb = full_bar(i);
+                            mbar_expect_tx(fb, bytes);
+                            tma_load_2d(sA + i * C::kABytes, &tm_a, fb, (kb0 + i) * C::kBK, a_row0);
+                            bulk_load(sSfa + i * C::kSfaBytes,
+                                p.sfa + (static_cast<int64_t>(a_row0 / 128) * p.kb_total + kb0 + i) * 512, 512, fb);
+                        }
+                        griddep_wait();
+                        for (int i = 0; i < npre; ++i) {
+                            uint32_t const fb = full_bar(i);
+                            tma_load_2d(sB + i * C::kBBytes, &tm_b, fb, (kb0 + i) * C::kBK, b_coord);
+                            for (int j = 0; j < sfb_atoms; ++j)
+                                bulk_load(sSfb + i * C::kSfbBytes + j * 512,
+                                    sfb_base + (static_cast<int64_t>(b_row0 / 128 + j) * p.kb_total + kb0 + i) * 512,
+                                    512, fb);
+                        }
+                        kb0 += npre;
+                        stage = npre == S ? 0 : npre;
+                        phase = npre == S ? 1u : 0u;
+                    }
+                }
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait_or_abort(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         record_abort(FSO_DEV_WAIT_PRODUCER, abort_flag);
@@ -306,6 +339,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------------------------------------------------------------ epilogue
+        if constexpr (kSwap) griddep_wait();              // before this kernel's first global store
         int const ew = warp - 4;
         int const quarter = warp & 3;
         int const half = ew >> 2;
@@ -524,6 +558,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float4* __restrict__ ws, uint2* __restrict__ out,
     int64_t quads, int splits)
 {
+    griddep_launch_dependents();
+    griddep_wait();                                       // the partials are the preceding kernel's output
     int64_t const i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= quads) return;
     float4 acc = ws[i];

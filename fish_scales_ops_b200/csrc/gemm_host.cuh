@@ -135,6 +135,26 @@ inline int ensure_smem_attr(Kernel kernel, int smem_bytes, std::atomic<uint64_t>
     return 0;
 }
 
+// FSO_B200_PDL=0 launches the decode-sized kernels without programmatic dependent launch (plain stream order).
+inline bool pdl_enabled()
+{
+    static int const v = [] {
+        const char* e = getenv("FSO_B200_PDL");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    return v != 0;
+}
+
+// The launch attribute that lets a kernel start while its predecessor in the stream is still running (the kernel
+// itself waits, with griddepcontrol.wait, before it touches anything the predecessor may produce).
+inline int pdl_attribute(cudaLaunchAttribute* attr)
+{
+    if (!pdl_enabled()) return 0;
+    attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr->val.programmaticStreamSerializationAllowed = 1;
+    return 1;
+}
+
 template <int BN, int EPI, bool kSwap, bool kGrouped>
 inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int grid,
     cudaStream_t stream)
@@ -144,7 +164,19 @@ inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmPa
     auto kernel = gemm_mxf8_kernel<BN, EPI, kSwap, kGrouped>;
     int const rc = ensure_smem_attr(kernel, C::kSmemBytes, done);
     if (rc != 0) return rc;
-    kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ta, tb, p);
+    if constexpr (kSwap) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+        cfg.blockDim = dim3(C::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_attribute(&attr[0]);
+        FSO_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
+    } else {
+        kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(ta, tb, p);
+    }
     return launch_status("gemm_mxf8_kernel");
 }
 
@@ -208,8 +240,9 @@ inline int launch_gemm_cluster(CUtensorMap const& ta, CUtensorMap const& tb, Gem
 {
     auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false>;
     cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cluster_launch_config<BN>(cfg, attr, items, p.splits, stream);
+    cfg.numAttrs += pdl_attribute(&attr[1]);
     FSO_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
     return launch_status("gemm_mxf8_kernel (cluster split-K)");
 }
@@ -385,8 +418,15 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     if (rc != 0) return rc;
     if (partial) {
         int64_t const quads = m * n / 4;
-        splitk_reduce_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, stream>>>(
-            static_cast<const float4*>(ws), static_cast<uint2*>(d), quads, splits);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>((quads + 255) / 256), 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        cfg.attrs = attr;
+        cfg.numAttrs = pl.swap ? pdl_attribute(&attr[0]) : 0;
+        FSO_CUDA(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float4*>(ws), static_cast<uint2*>(d),
+            quads, splits));
         rc = launch_status("splitk_reduce_kernel");
     }
     return rc;

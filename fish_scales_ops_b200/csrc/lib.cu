@@ -79,6 +79,25 @@ int fso_quantize_1x32(const void* x, void* xq, void* sf, int64_t m, int64_t k, i
     return launch_quantize_1x32(x, xq, sf, m, k, interleave_i, as_stream(stream));
 }
 
+int fso_quantize_activation_1x32(const void* x, void* xq, void* sf, int64_t m, int64_t k, void* stream)
+{
+    FSO_REQUIRE(m >= 0 && k > 0 && k % 128 == 0, "fso_quantize_activation_1x32: K = %lld must be a positive multiple of 128",
+        static_cast<long long>(k));
+    if (m == 0) return 0;
+    FSO_REQUIRE(x && xq && sf, "fso_quantize_activation_1x32: NULL pointer");
+    FSO_REQUIRE(aligned16(x) && aligned16(xq) && (reinterpret_cast<uintptr_t>(sf) & 3u) == 0,
+        "fso_quantize_activation_1x32: x and xq must be 16-byte aligned and sf 4-byte aligned");
+    return launch_quantize_1x32(x, xq, sf, m, k, 0, as_stream(stream), true);
+}
+
+__global__ void stream_fence_kernel() {}
+
+int fso_stream_fence(void* stream)
+{
+    stream_fence_kernel<<<1, 1, 0, as_stream(stream)>>>();
+    return launch_status("stream_fence_kernel");
+}
+
 int fso_requant_bs128_to_mx(const void* wq, const float* s128, void* out_q, void* out_sf, int64_t n, int64_t k,
     int64_t interleave_i, void* stream)
 {

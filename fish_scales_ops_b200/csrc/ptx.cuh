@@ -248,6 +248,23 @@ __device__ __forceinline__ void tmem_ld_wait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ------------------------------------------------------------------------------- programmatic dependent launch
+
+// Lets the next kernel of the stream, if it was launched with the programmatic-serialization attribute, start once
+// every CTA of this grid has executed this (or exited). That kernel must not touch what this one reads or writes
+// before its own griddep_wait().
+__device__ __forceinline__ void griddep_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Returns once the grids this one depends on have completed and their memory is visible; at once when the kernel
+// was launched without a programmatic dependency.
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------------- CTA pairs
 
 // The forms below serve the kernel that runs one 256-row MMA across a cluster of two CTAs (cta_group::2): each CTA

@@ -8,6 +8,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace fso {
 
@@ -90,8 +91,10 @@ __device__ __forceinline__ uint32_t word_from_16lanes(uint32_t byte, int sub16)
 // kUnroll independent 16-byte loads per thread are in flight. Rows in [m, m_pad) only get their zero words.
 template <int kUnroll>
 __global__ void __launch_bounds__(256) quantize_1x32_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
-    uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i)
+    uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i, uint32_t early)
 {
+    // activation form: a GEMM launched behind this kernel may start loading its weights while this one runs
+    if (early) griddep_launch_dependents();
     // 32-bit index arithmetic throughout (the launcher refuses more than 2^31 chunks): one division per thread.
     uint32_t const sub = threadIdx.x & 15;
     uint32_t const half = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
@@ -172,8 +175,9 @@ __device__ __forceinline__ uint32_t word_from_8lanes(uint32_t byte, uint32_t sub
 
 template <int kUnroll>
 __global__ void __launch_bounds__(256) quantize_1x32_wide_kernel(const uint8_t* __restrict__ x, uint4* __restrict__ q,
-    uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i)
+    uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i, uint32_t early)
 {
+    if (early) griddep_launch_dependents();
     uint32_t const sub = threadIdx.x & 7;
     uint32_t const oct = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;      // 8 lanes per 128-element chunk
     uint32_t const total = m_pad * kb;
@@ -216,8 +220,10 @@ __global__ void __launch_bounds__(256) quantize_1x32_wide_kernel(const uint8_t* 
     }
 }
 
+// early: the activation form, which lets a decode GEMM launched behind it (programmatic dependent launch) read its
+// weights while this kernel runs. Never for a call whose output the next kernel uses as a weight.
 inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int64_t k, int64_t interleave_i,
-    cudaStream_t stream)
+    cudaStream_t stream, bool early = false)
 {
     constexpr int kUnroll = 4;
     int64_t const m_pad = (m + 127) / 128 * 128;
@@ -235,12 +241,12 @@ inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int
         int64_t const wblocks = (octs * 8 + 255) / 256;
         quantize_1x32_wide_kernel<kWide><<<static_cast<unsigned>(wblocks), 256, 0, stream>>>(
             static_cast<const uint8_t*>(x), static_cast<uint4*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(m),
-            static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i));
+            static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i), early ? 1u : 0u);
         return launch_status("fso_quantize_1x32");
     }
     quantize_1x32_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
         static_cast<const uint4*>(x), static_cast<uint2*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(m),
-        static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i));
+        static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i), early ? 1u : 0u);
     return launch_status("fso_quantize_1x32");
 }
 

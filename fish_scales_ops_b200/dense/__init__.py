@@ -107,6 +107,14 @@ def _format_error(format, where: str) -> Exception:
                       f"weight, or a float8_e4m3fn weight with its MXFP8 scales)")
 
 
+def _complete(handle: DenseWeight) -> DenseWeight:
+    """One empty plain launch after the kernels that wrote the handle's tensors
+    (python/fish_scales_ops/dense/__init__.py:605-620): a decode linear issued right after starts loading its weights
+    before its predecessor on the stream has finished, which is only safe when that predecessor did not write them."""
+    _ops.stream_fence(handle.weight.device)
+    return handle
+
+
 def prepare_weight(w, *, format, scale=None) -> DenseWeight:
     """Prepare one dense weight ``[N, K]`` for this device, once, at load time
     (python/fish_scales_ops/dense/__init__.py:465-602).
@@ -152,7 +160,7 @@ def prepare_weight(w, *, format, scale=None) -> DenseWeight:
 
     if not is_fp8:
         q, sq = _ops.quantize_1x32_fp8(wd)
-        return DenseWeight("mxfp8", fmt, arch, k, n, q, sq)
+        return _complete(DenseWeight("mxfp8", fmt, arch, k, n, q, sq))
 
     if fmt == "bsfp8":
         want = (n // 128, kb)
@@ -162,7 +170,7 @@ def prepare_weight(w, *, format, scale=None) -> DenseWeight:
         if scale.device != w.device:
             raise ValueError(f"{ctx}: scale is on {scale.device} and the weight on {w.device}")
         q, sq = _ops.requant_block_fp8(wd.contiguous(), scale.detach().contiguous())
-        return DenseWeight("mxfp8", fmt, arch, k, n, q, sq)
+        return _complete(DenseWeight("mxfp8", fmt, arch, k, n, q, sq))
 
     # fmt == "mxfp8" with a float8_e4m3fn checkpoint
     if not isinstance(scale, torch.Tensor):
@@ -188,7 +196,7 @@ def prepare_weight(w, *, format, scale=None) -> DenseWeight:
             if e8m0 is not None and scale.dtype == e8m0 else ""
         raise ValueError(f"{ctx}: the MXFP8 scale must be uint8 [N, K/32] or int32 atom-layout words, got "
                          f"{scale.dtype}{hint}")
-    return DenseWeight("mxfp8", fmt, arch, k, n, _aligned_storage(wd.contiguous()), _aligned_storage(sq, 32))
+    return _complete(DenseWeight("mxfp8", fmt, arch, k, n, _aligned_storage(wd.contiguous()), _aligned_storage(sq, 32)))
 
 
 # ------------------------------------------------------------------------------------------------ activation contract
@@ -386,7 +394,7 @@ def _dense_linear_op(x, weight, scale, kind, bias=None, x_scale=None, residual=N
     if has_epi:
         _refuse_epilogue(op)
     if x_scale is None:
-        x, x_scale = _ops.quantize_1x32_fp8(x)
+        x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
     return _ops.linear_mxfp8(x, weight, x_scale, scale)
 
 
@@ -425,9 +433,9 @@ def _dense_linear_quantized_op(x, weight, scale, kind, bias=None, x_scale=None, 
     if has_epi:
         _refuse_epilogue(op)
     if x_scale is None:
-        x, x_scale = _ops.quantize_1x32_fp8(x)
+        x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
     y = _ops.linear_mxfp8(x, weight, x_scale, scale)
-    return _ops.quantize_1x32_fp8(y)
+    return _ops.quantize_1x32_fp8(y, activation=True)
 
 
 @_dense_linear_quantized_op.register_fake
@@ -465,7 +473,7 @@ def _dense_quantize_activation_op(x):
     m = int(x2.shape[0])
     if m == 0:
         return (x.new_empty((0, k), dtype=FP8), _empty_act_scale(0, k, x.device))
-    return _ops.quantize_1x32_fp8(x2)
+    return _ops.quantize_1x32_fp8(x2, activation=True)
 
 
 @_dense_quantize_activation_op.register_fake

@@ -43,6 +43,19 @@ int fso_b200_device_status(int* status);
 int fso_quantize_1x32(const void* x_bf16, void* xq, void* sf, int64_t m, int64_t k, int64_t interleave_i,
                       void* stream);
 
+/* The activation form of fso_quantize_1x32 (no row interleave): the same bytes, and the kernel lets a decode-sized
+ * fso_gemm_mxfp8 launched behind it on the stream start loading its weights while it runs (programmatic dependent
+ * launch; the GEMM waits for this kernel before it reads xq / sf). Do not use it to produce a tensor that the next
+ * kernel on the stream reads as a weight. Replaces: dense_quantize_activation,
+ * python/fish_scales_ops/dense/__init__.py:1068-1099 (and the quantize step inside dense_linear, :911-932). */
+int fso_quantize_activation_1x32(const void* x, void* xq, void* sf, int64_t m, int64_t k, void* stream);
+
+/* One empty plain launch: everything enqueued before it has completed before anything enqueued after it starts,
+ * including kernels that use programmatic dependent launch. fso.dense.prepare_weight ends with it, so that a linear
+ * issued right after prepare never reads weight bytes that are still being written.
+ * Replaces: _complete_handle, python/fish_scales_ops/dense/__init__.py:605-620. */
+int fso_stream_fence(void* stream);
+
 /* Block-FP8 checkpoint (e4m3 [N, K] + one fp32 scale per 128x128 tile, [N/128, K/128]) -> MXFP8: each value is
  * bf16_rne(float(fp8) * scale) and then goes through the 1x32 rule. N % 128 == 0. interleave_i as in
  * fso_quantize_1x32 (stacked experts, I % 128 == 0; the tile scale follows the source row).

@@ -279,3 +279,69 @@ def test_cluster_split_k_equals_workspace_split_k(fso, oracle, device_ok):
     weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
     ref = _oracle_out(oracle, x, inputs.to_np_u8(weight.weight), inputs.to_np_u32(weight.scale))
     inputs.assert_close_to_oracle(cluster[shapes[0]], ref, "cluster split-K vs oracle")
+
+
+_CHAIN_CHILD = r"""
+import sys, torch
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+import inputs
+import fish_scales_ops_b200 as fso
+from fish_scales_ops_b200 import _ops
+dims = [1024, 2048, 1024, 4096, 512, 2048]
+ws = [fso.dense.prepare_weight(inputs.weight(dims[i + 1], dims[i], 90 + i).cuda(), format="mxfp8")
+      for i in range(len(dims) - 1)]
+outs = {}
+for m in (1, 16, 40):
+    x = inputs.activation(m, dims[0], 80 + m).cuda()
+    def chain():
+        h, keep = x, []
+        for w in ws:
+            h = fso.dense.linear(h, w)          # quantizer + decode GEMM, each GEMM reads what the last one wrote
+            keep.append(h)
+        xq, sx = fso.dense.quantize_activation(x)
+        for _ in range(3):                       # pre-quantized form: GEMM directly behind GEMM
+            keep.append(fso.dense.linear(xq, ws[0], x_scale=sx))
+        return keep
+    eager = chain()
+    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            graphed = chain()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(eager, graphed):
+        assert torch.equal(a, b), "graph replay differs from eager"
+    outs[m] = [t.cpu() for t in eager]
+assert _ops.device_status() == 0
+torch.save(outs, sys.argv[1] + ".pt")
+print("ok")
+"""
+
+
+def test_dependent_launch_chain_equals_plain_launches(fso, device_ok):
+    """Decode-sized GEMMs are launched with programmatic dependent launch: a GEMM starts its set-up and weight loads
+    while its predecessor (the activation quantizer or the previous GEMM) still runs, and waits for it before reading
+    activations or writing. A chain in which every linear consumes the previous one's output, eager and under CUDA-graph
+    replay, must give the bytes of the same chain with plain launches (FSO_B200_PDL=0)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tmp = os.path.join(root, "gpurun_out")
+    os.makedirs(tmp, exist_ok=True)
+    got = {}
+    for pdl in ("1", "0"):
+        base = os.path.join(tmp, f"chain_pdl{pdl}")
+        res = subprocess.run([sys.executable, "-c", _CHAIN_CHILD % (root, os.path.join(root, "tests")), base],
+                             env=dict(os.environ, FSO_B200_PDL=pdl), capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
+        got[pdl] = torch.load(base + ".pt")
+        os.remove(base + ".pt")
+    for m in got["1"]:
+        for a, b in zip(got["1"][m], got["0"][m]):
+            assert torch.equal(a, b), m
