@@ -7,6 +7,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -93,8 +95,12 @@ template <int kUnroll>
 __global__ void __launch_bounds__(256) quantize_1x32_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
     uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i, uint32_t early)
 {
-    // activation form: a GEMM launched behind this kernel may start loading its weights while this one runs
-    if (early) griddep_launch_dependents();
+    // activation form: a GEMM launched behind this kernel may start loading its weights while this one runs, and
+    // this kernel itself may have been started under its predecessor, whose output x may be
+    if (early) {
+        griddep_launch_dependents();
+        griddep_wait();
+    }
     // 32-bit index arithmetic throughout (the launcher refuses more than 2^31 chunks): one division per thread.
     uint32_t const sub = threadIdx.x & 15;
     uint32_t const half = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
@@ -177,7 +183,10 @@ template <int kUnroll>
 __global__ void __launch_bounds__(256) quantize_1x32_wide_kernel(const uint8_t* __restrict__ x, uint4* __restrict__ q,
     uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb, uint32_t interleave_i, uint32_t early)
 {
-    if (early) griddep_launch_dependents();
+    if (early) {
+        griddep_launch_dependents();
+        griddep_wait();
+    }
     uint32_t const sub = threadIdx.x & 7;
     uint32_t const oct = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;      // 8 lanes per 128-element chunk
     uint32_t const total = m_pad * kb;
@@ -220,6 +229,15 @@ __global__ void __launch_bounds__(256) quantize_1x32_wide_kernel(const uint8_t* 
     }
 }
 
+inline bool quantizer_pdl_enabled()
+{
+    static int const v = [] {
+        const char* e = getenv("FSO_B200_PDL");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    return v != 0;
+}
+
 // early: the activation form, which lets a decode GEMM launched behind it (programmatic dependent launch) read its
 // weights while this kernel runs. Never for a call whose output the next kernel uses as a weight.
 inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int64_t k, int64_t interleave_i,
@@ -235,18 +253,32 @@ inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int
             static_cast<long long>(m), static_cast<long long>(k));
         return FSO_ERR_INVALID;
     }
+    // the activation form is itself launched with the programmatic-serialization attribute (it waits at its top)
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (early && quantizer_pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
     if ((reinterpret_cast<uintptr_t>(x) & 31u) == 0) {
         constexpr int kWide = 2;
         int64_t const octs = (m_pad * kb + kWide - 1) / kWide;
         int64_t const wblocks = (octs * 8 + 255) / 256;
-        quantize_1x32_wide_kernel<kWide><<<static_cast<unsigned>(wblocks), 256, 0, stream>>>(
-            static_cast<const uint8_t*>(x), static_cast<uint4*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(m),
-            static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i), early ? 1u : 0u);
+        cfg.gridDim = dim3(static_cast<unsigned>(wblocks), 1, 1);
+        FSO_CUDA(cudaLaunchKernelEx(&cfg, quantize_1x32_wide_kernel<kWide>, static_cast<const uint8_t*>(x),
+            static_cast<uint4*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(m), static_cast<uint32_t>(m_pad),
+            static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i), early ? 1u : 0u));
         return launch_status("fso_quantize_1x32");
     }
-    quantize_1x32_kernel<kUnroll><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        static_cast<const uint4*>(x), static_cast<uint2*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(m),
-        static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i), early ? 1u : 0u);
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    FSO_CUDA(cudaLaunchKernelEx(&cfg, quantize_1x32_kernel<kUnroll>, static_cast<const uint4*>(x), static_cast<uint2*>(q),
+        static_cast<uint32_t*>(sf), static_cast<uint32_t>(m), static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb),
+        static_cast<uint32_t>(interleave_i), early ? 1u : 0u));
     return launch_status("fso_quantize_1x32");
 }
 
