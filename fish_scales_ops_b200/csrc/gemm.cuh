@@ -66,13 +66,17 @@ struct GemmCfg {
     static constexpr int kSfbAtoms = BN > 128 ? BN / 128 : 1;
     static constexpr int kSfbBytes = 512 * kSfbAtoms;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-    static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - 512 /*barriers*/;
-    // EPI_CLUSTER keeps room for the other slices' accumulators: [slice - 1][BN columns][128 rows] fp32
-    static constexpr int kRedSlices = EPI != 3 /* EPI_CLUSTER */ ? 0 : BN <= 16 ? 7 : BN <= 32 ? 6 : 2;
-    static constexpr int kRedBytes = kRedSlices * BN * 512;
-    static constexpr int kStagesMax = (kSmemBudget - kRedBytes) / kStageBytes;
-    static constexpr int kStages = EPI == 3 ? (kStagesMax > 6 ? 6 : kStagesMax) : kStagesMax > 12 ? 12 : kStagesMax;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kRedBytes;
+    // Token tiles of 64 and fewer (the swapped, decode-sized kernels) take half an SM's shared memory, so that two
+    // CTAs share an SM: every tile of a 1.5-wave problem is resident at once, and under programmatic dependent launch
+    // the next kernel's CTAs load weights beside the last CTAs of this one.
+    static constexpr bool kTwoPerSm = BN <= 64;
+    static constexpr int kSmemBudget = (kTwoPerSm ? 113 : 227) * 1024 - 1024 /*alignment slack*/ - 512 /*barriers*/;
+    static constexpr int kStagesMax = kSmemBudget / kStageBytes;
+    static constexpr int kStages = kStagesMax > 12 ? 12 : kStagesMax;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+    // EPI_CLUSTER: the other slices' accumulators, [slice - 1][BN columns][128 rows] fp32, land in CTA 0's stage
+    // buffers once its own main loop is over
+    static constexpr int kRedSlices = (kStages * kStageBytes) / (BN * 512);
     // tensor-memory columns: accumulators first, then two alternating scale-factor buffers
     static constexpr int kAccCols = kAccStages * BN;
     static constexpr int kSfaCols = 4;
@@ -83,7 +87,7 @@ struct GemmCfg {
         : kColsUsed <= 256 ? 256 : 512;
     static_assert(kColsUsed <= 512, "tensor memory budget");
     static_assert(kStages >= 3, "pipeline depth");
-    static_assert(kSmemBytes > 116 * 1024, "one CTA per SM is assumed by the tensor-memory allocation");
+    static_assert(kSmemBytes > 116 * 1024 || kTmemCols <= 256, "CTAs that share an SM must share its 512 columns");
 };
 
 struct TileCoord {
@@ -167,7 +171,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t const misc_off = static_cast<uint32_t>(S) * C::kStageBytes + 8u * (2 * S + 4);
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gbase + misc_off);
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(gbase + misc_off + 4);
-    uint32_t const red_off = (misc_off + 16u + 15u) & ~15u;      // EPI_CLUSTER: the other slices' accumulators
+    constexpr uint32_t red_off = 0;       // EPI_CLUSTER: the other slices' accumulators reuse the stage buffers
     static_assert(EPI != EPI_CLUSTER || kSwap, "cluster split-K serves the swapped orientation");
     // EPI_CLUSTER: this thread's accumulator row (epilogue warps), kept in registers across the cluster barrier
     float red_v[EPI == EPI_CLUSTER ? BN : 1];
@@ -199,8 +203,6 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     uint32_t const tmem_base = *tmem_slot;
-    // first half of the "every CTA of the cluster has started" barrier; waited for before the first remote store
-    if constexpr (EPI == EPI_CLUSTER) cluster_arrive();
     // Decode-sized calls are chained with programmatic dependent launch: the next kernel may start its set-up and its
     // weight loads while this one runs, and this one has done the same under its predecessor. Before its
     // griddep_wait() a kernel reads only weights (immutable) and writes nothing outside its own CTA.
@@ -515,7 +517,10 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ------------------------------------------------------------------ split-K reduction inside the cluster
         uint32_t const rank = cluster_ctarank();
         int const row = (warp & 3) * 32 + lane;
-        cluster_wait();                                   // every CTA of the cluster is running
+        // Every thread of the cluster has left its main loop: the epilogue warps arrive after their accumulator is
+        // complete, so no MMA or TMA of CTA 0 still touches its stage buffers, which now receive the other slices.
+        cluster_arrive();
+        cluster_wait();
         if (warp >= 4 && red_have && rank != 0) {
 #pragma unroll
             for (int j = 0; j < BN; ++j)

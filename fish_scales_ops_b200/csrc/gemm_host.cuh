@@ -75,7 +75,9 @@ inline double wave_efficiency(int64_t items, int sms)
 // shared memory; 8 is the portable cluster size).
 inline int cluster_split_limit(int bn)
 {
-    return bn <= 16 ? 8 : bn <= 32 ? 7 : bn <= 64 ? 3 : 1;
+    int const slices = bn == 16 ? GemmCfg<16, EPI_CLUSTER>::kRedSlices : bn == 32 ? GemmCfg<32, EPI_CLUSTER>::kRedSlices
+        : bn == 64 ? GemmCfg<64, EPI_CLUSTER>::kRedSlices : 0;
+    return slices + 1 < 8 ? slices + 1 : 8;
 }
 
 inline void pick_splits(int64_t tiles, int kb, int sms, int min_kb, int max_s, int* splits, int* kb_per)
@@ -130,6 +132,9 @@ inline int ensure_smem_attr(Kernel kernel, int smem_bytes, std::atomic<uint64_t>
     uint64_t const bit = 1ull << (dev & 63);
     if ((done_mask.load(std::memory_order_acquire) & bit) == 0) {
         FSO_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        // all of the SM's configurable memory as shared memory: the half-SM kernels then fit two CTAs per SM
+        FSO_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+            static_cast<int>(cudaSharedmemCarveoutMaxShared)));
         done_mask.fetch_or(bit, std::memory_order_release);
     }
     return 0;
@@ -393,7 +398,8 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     p.splits = splits;
     p.kb_per_split = (p.kb_total + splits - 1) / splits;
     int64_t const items = static_cast<int64_t>(pl.tiles_a) * pl.tiles_b * splits;
-    int const grid = static_cast<int>(items < sms ? items : sms);
+    int const slots = pl.swap ? 2 * sms : sms;          // the swapped kernels run two CTAs per SM
+    int const grid = static_cast<int>(items < slots ? items : slots);
     if (in_cluster && !splitk_through_workspace()) {
         return pl.bn == 16 ? launch_gemm_cluster<16>(ta, tb, p, static_cast<int>(items), stream)
             : pl.bn == 32 ? launch_gemm_cluster<32>(ta, tb, p, static_cast<int>(items), stream)
