@@ -10,7 +10,7 @@ The compute lives in ``libfso_b200.so`` (hand-written CUDA behind the C ABI of `
 validates arguments, allocates outputs and passes pointers. There is no other backend and no CPU path.
 """
 from . import _build, _lib  # noqa: F401
-from . import dense, moe  # noqa: F401
+from . import compat, dense, moe  # noqa: F401
 
 __version__ = "0.1.0"
 

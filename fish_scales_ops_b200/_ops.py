@@ -164,6 +164,25 @@ def moe_combine(dn, slot, topk_w, bias, bias_scale, out):
                                     stream_ptr()), "fso_moe_combine")
 
 
+_LOGIT_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def moe_topk_from_logits(logits, topk: int, renormalize: bool, with_shared_gate: bool, n_valid, expert_map):
+    """logits [M, E (+1)] -> (ids int32 [M, topk], weights fp32 [M, topk], shared_gate fp32 [M] or [0])."""
+    m, width = int(logits.shape[0]), int(logits.shape[1])
+    e = width - (1 if with_shared_gate else 0)
+    dev = logits.device
+    with torch.cuda.device(dev):
+        ids = torch.empty((m, topk), dtype=torch.int32, device=dev)
+        w = torch.empty((m, topk), dtype=torch.float32, device=dev)
+        gate = torch.empty((m if with_shared_gate else 0,), dtype=torch.float32, device=dev)
+        check(lib().fso_moe_topk_from_logits(ptr(logits), _LOGIT_DTYPES[logits.dtype], m, e, int(logits.stride(0)),
+                                             int(topk), 1 if renormalize else 0, ptr(n_valid), ptr(expert_map),
+                                             ptr(ids), ptr(w), ptr(gate) if with_shared_gate else None,
+                                             stream_ptr()), "fso_moe_topk_from_logits")
+    return ids, w, gate
+
+
 def ep_plan_count(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
     """int32 [T, k] global ids -> (rank_mask int64 [T], row int64 [world + 1] = rows per destination rank, T)."""
     t, k = int(topk_ids.shape[0]), int(topk_ids.shape[1])

@@ -1,0 +1,86 @@
+"""The router in front of the MoE layer, under the names the reference exports them
+(python/fish_scales_ops/gemm/mxfp8.py:1355-1436, reached there as ``fso.compat.moe_topk_from_logits`` and
+``fso.compat.moe_router_topk``): softmax over the experts, top-k selection, renormalization, the padded-row
+sentinel of a CUDA-graph bucket, the expert-parallel id map and the shared expert's gate in one kernel."""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _ops
+from ._arch import SERVED_MAJOR, arch_label, device_arch
+
+__all__ = ["moe_topk_from_logits", "moe_router_topk"]
+
+_MAX_EXPERTS = 1024
+_MAX_TOPK = 8
+
+
+@torch.library.custom_op(
+    "fish_scales_ops::moe_topk_from_logits",
+    mutates_args=(),
+    schema="(Tensor logits, int topk, bool renormalize=True, bool with_shared_gate=False, "
+           "Tensor? num_token_non_padded=None, Tensor? expert_map=None) -> (Tensor, Tensor, Tensor)",
+)
+def _topk_from_logits_op(logits, topk, renormalize=True, with_shared_gate=False, num_token_non_padded=None,
+                         expert_map=None):
+    """Body of ``torch.ops.fish_scales_ops.moe_topk_from_logits`` (csrc/gemm/ops/moe_glue.cu:3074-3152): the same
+    refusals, before anything is launched."""
+    op = f"fish_scales_ops::moe_topk_from_logits ({arch_label(device_arch())})"
+    if not logits.is_cuda or logits.dim() != 2:
+        raise ValueError(f"{op}: logits must be a CUDA [M, E] tensor")
+    if logits.stride(1) != 1:
+        raise ValueError(f"{op}: logits must have a contiguous expert dimension")
+    if logits.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise ValueError(f"{op}: logits must be bf16, fp16 or fp32, got {logits.dtype}")
+    if device_arch() // 10 != SERVED_MAJOR:
+        raise NotImplementedError(f"{op}: this build serves sm_100-family devices")
+    e = int(logits.shape[1]) - (1 if with_shared_gate else 0)
+    if not 1 <= e <= _MAX_EXPERTS:
+        raise ValueError(f"{op}: num_experts must be in [1, {_MAX_EXPERTS}], got {e}")
+    if not (1 <= topk <= _MAX_TOPK and topk <= e):
+        raise ValueError(f"{op}: topk must be in [1, min({_MAX_TOPK}, num_experts)], got {topk}")
+    n_valid = None
+    if num_token_non_padded is not None and num_token_non_padded.numel() > 0:
+        n_valid = num_token_non_padded
+        if not n_valid.is_cuda or n_valid.dtype != torch.int32 or n_valid.numel() != 1:
+            raise ValueError(f"{op}: num_token_non_padded must be a CUDA int32 tensor with one element")
+    emap = None
+    if expert_map is not None and expert_map.numel() > 0:
+        emap = expert_map
+        if not emap.is_cuda or emap.dtype != torch.int32 or not emap.is_contiguous():
+            raise ValueError(f"{op}: expert_map must be a contiguous CUDA int32 tensor")
+        if emap.numel() < e + 1:
+            raise ValueError(f"{op}: expert_map must have num_experts + 1 entries (the last one maps the padded-row "
+                             f"sentinel)")
+    return _ops.moe_topk_from_logits(logits, int(topk), bool(renormalize), bool(with_shared_gate), n_valid, emap)
+
+
+@_topk_from_logits_op.register_fake
+def _topk_from_logits_fake(logits, topk, renormalize=True, with_shared_gate=False, num_token_non_padded=None,
+                           expert_map=None):
+    m = logits.shape[0]
+    return (logits.new_empty((m, topk), dtype=torch.int32), logits.new_empty((m, topk), dtype=torch.float32),
+            logits.new_empty((m if with_shared_gate else 0,), dtype=torch.float32))
+
+
+def moe_topk_from_logits(logits: torch.Tensor, topk: int, *, renormalize: bool = True, with_shared_gate: bool = False,
+                         num_token_non_padded: Optional[torch.Tensor] = None,
+                         expert_map: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Router logits ``[M, num_experts]`` (``num_experts + 1`` columns with ``with_shared_gate``; bf16, fp16 or fp32)
+    -> ``(topk_ids int32 [M, topk], topk_w fp32 [M, topk], shared_gate fp32 [M] or empty)``, one launch. Ids come
+    out in descending weight order, ties broken toward the lower expert id; ``renormalize`` divides the selected
+    probabilities by their own sum, otherwise the weights are the plain softmax over all experts; rows at or past
+    ``num_token_non_padded`` get the sentinel id ``num_experts`` (through ``expert_map`` when given) and weight
+    zero; ``expert_map`` int32 ``[num_experts + 1]`` maps global ids to an expert-parallel rank's local ids."""
+    return torch.ops.fish_scales_ops.moe_topk_from_logits(logits, int(topk), bool(renormalize), bool(with_shared_gate),
+                                                          num_token_non_padded, expert_map)
+
+
+def moe_router_topk(hidden: torch.Tensor, router_weight: torch.Tensor, topk: int, *, renormalize: bool = True,
+                    with_shared_gate: bool = False, num_token_non_padded: Optional[torch.Tensor] = None,
+                    expert_map: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The whole router in two launches: the logit GEMM (a plain library GEMM, as in the reference: the gate matrix
+    is a megabyte) and :func:`moe_topk_from_logits`. ``router_weight`` bf16 ``[num_experts (+1), HIDDEN]``."""
+    logits = torch.nn.functional.linear(hidden, router_weight)
+    return moe_topk_from_logits(logits, topk, renormalize=renormalize, with_shared_gate=with_shared_gate,
+                                num_token_non_padded=num_token_non_padded, expert_map=expert_map)

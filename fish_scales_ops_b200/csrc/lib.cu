@@ -40,6 +40,7 @@ int sm_count()
 #include "gemm_host.cuh"
 #include "moe.cuh"
 #include "exchange.cuh"
+#include "router.cuh"
 
 using namespace fso;
 
@@ -418,6 +419,34 @@ int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const f
     combine_sparse_kernel<8><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, as_stream(stream)>>>(
         static_cast<const uint8_t*>(dn), slot_of_flat, topk_w, tokens, static_cast<int>(topk), static_cast<int>(h * 2), sc);
     return launch_status("combine_sparse_kernel");
+}
+
+int fso_moe_topk_from_logits(const void* logits, int64_t logit_dtype, int64_t m, int64_t num_experts, int64_t ld,
+    int64_t topk, int64_t renormalize, const int32_t* num_token_non_padded, const int32_t* expert_map,
+    int32_t* topk_ids, float* topk_w, float* shared_gate, void* stream)
+{
+    FSO_REQUIRE(m >= 0 && m < (1ll << 31), "fso_moe_topk_from_logits: M out of range");
+    FSO_REQUIRE(num_experts >= 1 && num_experts <= kRouterMaxExperts,
+        "fso_moe_topk_from_logits: num_experts must be in [1, %d], got %lld", kRouterMaxExperts,
+        static_cast<long long>(num_experts));
+    FSO_REQUIRE(topk >= 1 && topk <= kRouterMaxTopk && topk <= num_experts,
+        "fso_moe_topk_from_logits: topk must be in [1, min(%d, num_experts)], got %lld", kRouterMaxTopk,
+        static_cast<long long>(topk));
+    FSO_REQUIRE(ld >= num_experts + (shared_gate != nullptr ? 1 : 0),
+        "fso_moe_topk_from_logits: the row stride %lld is shorter than a row", static_cast<long long>(ld));
+    FSO_REQUIRE(logit_dtype >= 0 && logit_dtype <= 2, "fso_moe_topk_from_logits: logits must be bf16 (0), fp16 (1) or fp32 (2)");
+    if (m == 0) return 0;
+    FSO_REQUIRE(logits && topk_ids && topk_w, "fso_moe_topk_from_logits: NULL pointer");
+    cudaStream_t const st = as_stream(stream);
+    bool const rn = renormalize != 0;
+    if (logit_dtype == 0)
+        return launch_router_topk<__nv_bfloat16>(logits, ld, m, num_experts, topk, rn, num_token_non_padded, expert_map,
+            topk_ids, topk_w, shared_gate, st);
+    if (logit_dtype == 1)
+        return launch_router_topk<__half>(logits, ld, m, num_experts, topk, rn, num_token_non_padded, expert_map,
+            topk_ids, topk_w, shared_gate, st);
+    return launch_router_topk<float>(logits, ld, m, num_experts, topk, rn, num_token_non_padded, expert_map, topk_ids,
+        topk_w, shared_gate, st);
 }
 
 int fso_ep_plan_count(const int32_t* topk_ids, int64_t tokens, int64_t topk, int64_t experts_per_rank, int64_t world,

@@ -132,6 +132,18 @@ int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2,
 int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,
                     const float* bias_scale, void* out, int64_t tokens, int64_t topk, int64_t h, void* stream);
 
+/* Router: logits [M, ld] (bf16 = 0, fp16 = 1, fp32 = 2; expert dimension contiguous) -> topk_ids int32 [M, topk] in
+ * descending weight order (ties to the lower expert id), topk_w fp32 [M, topk] = softmax over the selected k
+ * (renormalize != 0) or the plain softmax over all experts. Rows at or past *num_token_non_padded (device int32,
+ * may be NULL) get the sentinel id num_experts and weight 0; expert_map (device int32 [num_experts + 1], may be
+ * NULL) is applied to every id including the sentinel; shared_gate (fp32 [M], may be NULL) = sigmoid of logit
+ * column num_experts. num_experts <= 1024, topk <= 8.
+ * Replaces: moe_topk_from_logits, csrc/gemm/ops/moe_glue.cu:3074-3152 (kernel :1370-1465). */
+int fso_moe_topk_from_logits(const void* logits, int64_t logit_dtype, int64_t m, int64_t num_experts, int64_t ld,
+                             int64_t topk, int64_t renormalize, const int32_t* num_token_non_padded,
+                             const int32_t* expert_map, int32_t* topk_ids, float* topk_w, float* shared_gate,
+                             void* stream);
+
 /* ---- Expert-parallel exchange over peer memory -------------------------------------------------------------------
  * The reference has no communication code: docs/guide.md:139-141 and python/fish_scales_ops/moe/__init__.py:733-739
  * leave sharding and the exchange to the caller. The entry points below have no counterpart there; they serve

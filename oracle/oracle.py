@@ -250,3 +250,44 @@ def moe_layer(hidden, w13_q, w13_sf, w2_q, w2_sf, topk_ids, topk_w, interleaved:
         dn = (dd @ w2d.t()).to(torch.bfloat16).to(torch.float32)
         out.index_add_(0, torch.from_numpy(tok), dn * torch.from_numpy(wts[tok, slot])[:, None])
     return out
+
+
+# ------------------------------------------------------------------------------------------------------- router
+
+def router_topk(logits, topk: int, renormalize: bool = True, with_shared_gate: bool = False, n_valid=None,
+                expert_map=None):
+    """CPU statement of the router (csrc/gemm/ops/moe_glue.cu:1253-1465 of the reference): per token, k picks of the
+    largest remaining logit (ties to the lower expert id), weights exp(l - max) over the selected experts, summed in
+    pick order in fp32, divided by that sum (``renormalize``) or by the fp32 sum of exp(l - max) over all experts;
+    rows at or past ``n_valid`` get the sentinel id E and weight 0; ``expert_map`` [E + 1] is applied to every id;
+    the shared gate is sigmoid of logit column E. ``logits``: torch tensor [M, E (+1)] of bf16 / fp16 / fp32.
+    Returns (ids int32 [M, k], weights fp32 [M, k], gate fp32 [M] or [0]). Ids are exact; the weights depend on the
+    exp implementation and are a tolerance oracle (1e-5 relative in the reference's own test,
+    tests/gemm/unit/test_moe_router_topk.py:20-25)."""
+    lg = logits.detach().cpu().to(torch.float32).numpy()
+    m, width = lg.shape
+    e = width - (1 if with_shared_gate else 0)
+    ids = np.zeros((m, topk), np.int32)
+    w = np.zeros((m, topk), np.float32)
+    gate = np.zeros((m if with_shared_gate else 0,), np.float32)
+    emap = None if expert_map is None else np.asarray(
+        expert_map.detach().cpu().numpy() if isinstance(expert_map, torch.Tensor) else expert_map, np.int32)
+    for t in range(m):
+        if with_shared_gate:
+            gate[t] = np.float32(1.0) / (np.float32(1.0) + np.exp(-lg[t, e], dtype=np.float32))
+        if n_valid is not None and t >= int(n_valid):
+            ids[t, :] = e if emap is None else emap[e]
+            continue
+        row = lg[t, :e]
+        # stable sort of -logit: descending value, ascending id among equals
+        order = np.argsort(-row, kind="stable")[:topk]
+        sel = row[order]
+        ex = np.exp(sel - sel[0], dtype=np.float32)
+        denom = np.float32(0.0)
+        for j in range(topk):
+            denom = np.float32(denom + ex[j])
+        if not renormalize:
+            denom = np.exp(row - sel[0], dtype=np.float32).sum(dtype=np.float32)
+        w[t] = ex * (np.float32(1.0) / denom)
+        ids[t] = order if emap is None else emap[order]
+    return ids, w, gate

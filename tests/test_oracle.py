@@ -143,3 +143,26 @@ def test_dense_oracle_tracks_bf16_masters(oracle):
     ref = x.float() @ w.float().t()
     cos = torch.nn.functional.cosine_similarity(y.flatten(), ref.flatten(), dim=0)
     assert cos > 0.999
+
+
+def test_router_oracle_matches_torch_softmax_topk(oracle):
+    """The router oracle against torch's softmax / topk on random fp32 logits (no ties): same ids in the same order,
+    weights to fp32 rounding, with and without renormalization; padded rows, map and gate by their definitions."""
+    import inputs
+
+    for m, e, k in ((64, 128, 8), (33, 1024, 8), (17, 256, 1), (9, 40, 5)):
+        lg = torch.randn(m, e + 1, generator=inputs.gen(3 * m + e), dtype=torch.float32) * 3.0
+        for renorm in (True, False):
+            ids, w, gate = oracle.router_topk(lg, k, renorm, True)
+            p = torch.softmax(lg[:, :e], dim=-1)
+            tw, ti = torch.topk(p, k, dim=-1)
+            if renorm:
+                tw = tw / tw.sum(dim=-1, keepdim=True)
+            assert np.array_equal(ids, ti.numpy().astype(np.int32))
+            assert float(np.abs(w - tw.numpy()).max()) <= 1e-5 * float(tw.max())
+            assert float(np.abs(gate - torch.sigmoid(lg[:, e]).numpy()).max()) <= 1e-6
+        emap = np.arange(e + 1, dtype=np.int32)[::-1].copy()
+        ids_m, w_m, _ = oracle.router_topk(lg[:, :e], k, True, False, m // 2, emap)
+        ids_p, _, _ = oracle.router_topk(lg[:, :e], k, True)
+        assert np.array_equal(ids_m[:m // 2], emap[ids_p[:m // 2]])
+        assert (ids_m[m // 2:] == emap[e]).all() and (w_m[m // 2:] == 0).all()
