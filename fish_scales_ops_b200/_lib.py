@@ -31,6 +31,8 @@ SIGNATURES = {
                            _c_p],
     "fso_moe_fc2": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p],
     "fso_moe_combine": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
+    "fso_gemm_mxfp8_epilogue": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_i64, _c_p, _c_i64,
+                                _c_p],
     "fso_quantize_activation_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_p],
     "fso_stream_fence": [_c_p],
     "fso_moe_topk_from_logits": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p,

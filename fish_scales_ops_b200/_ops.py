@@ -97,8 +97,10 @@ def gemm_ws_bytes(m: int, n: int, k: int) -> int:
     return int(v.value)
 
 
-def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.Tensor) -> torch.Tensor:
-    """bf16 [M, N] = xq [M, K] @ w [N, K]^T over MXFP8 operands (python/fish_scales_ops/gemm/mxfp8.py:90-188)."""
+def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.Tensor, bias=None, residual=None,
+                 activation: int = 0) -> torch.Tensor:
+    """bf16 [M, N] = xq [M, K] @ w [N, K]^T over MXFP8 operands (python/fish_scales_ops/gemm/mxfp8.py:90-188), with
+    the dense epilogue bf16(act(acc + bias) + residual) when any of its fields is given."""
     m, k = int(xq.shape[0]), int(xq.shape[1])
     n = int(w.shape[0])
     with torch.cuda.device(xq.device):
@@ -107,8 +109,13 @@ def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.
             return out
         ws_bytes = gemm_ws_bytes(m, n, k)
         ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=xq.device) if ws_bytes > 0 else None
-        check(lib().fso_gemm_mxfp8(ptr(xq), ptr(sx), ptr(w), ptr(sw), ptr(out), m, n, k, ptr(ws), ws_bytes,
-                                   stream_ptr()), "fso_gemm_mxfp8")
+        if bias is None and residual is None and activation == 0:
+            check(lib().fso_gemm_mxfp8(ptr(xq), ptr(sx), ptr(w), ptr(sw), ptr(out), m, n, k, ptr(ws), ws_bytes,
+                                       stream_ptr()), "fso_gemm_mxfp8")
+        else:
+            check(lib().fso_gemm_mxfp8_epilogue(ptr(xq), ptr(sx), ptr(w), ptr(sw), ptr(out), m, n, k, ptr(bias),
+                                                ptr(residual), int(activation), ptr(ws), ws_bytes, stream_ptr()),
+                  "fso_gemm_mxfp8_epilogue")
     return out
 
 

@@ -49,7 +49,30 @@ struct GemmParams {
     int group_a;               // raster: tiles of A walked together before B advances
     int out_align32;           // the output base is 32-byte aligned (256-bit stores are usable)
     int64_t out_rows;          // rows of the output (row stride of one split's partial = out_rows * ldo)
+    // dense epilogue (kFused kernels and the split-K reduce): out = bf16(act(acc + bias[n]) + residual[m, n])
+    const __nv_bfloat16* bias;      // [N] or nullptr
+    const __nv_bfloat16* residual;  // [M, N] or nullptr
+    int act;                        // 0 = identity, 1 = erf-GELU
 };
+
+// The bias as the epilogue adds it: +0.0 becomes -0.0, so that a zero bias changes no accumulator value (not even
+// the sign of a zero) and bias = 0 gives the bytes of bias = None.
+__device__ __forceinline__ float bias_term(__nv_bfloat16 b)
+{
+    uint32_t const bits = static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16;
+    return __uint_as_float(bits == 0u ? 0x80000000u : bits);
+}
+
+// act(acc + bias) in fp32; erf-GELU as 0.5 v (1 + erf(v / sqrt 2)) with the constant rounded to fp32 first.
+__device__ __forceinline__ float epilogue_value(float acc, float bias_f, bool has_bias, int act)
+{
+    float v = has_bias ? acc + bias_f : acc;
+    if (act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+    return v;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 template <int BN, int EPI = 0>
 struct GemmCfg {
@@ -147,7 +170,9 @@ __device__ __forceinline__ float silu_mul(float g, float u)
     return (0.5f * g) * (1.f + t) * u;
 }
 
-template <int BN, int EPI, bool kSwap, bool kGrouped>
+// kFused: the bf16-writing epilogues also apply bias / activation / residual (separate instantiations, so that a call
+// without them runs the code it always ran).
+template <int BN, int EPI, bool kSwap, bool kGrouped, bool kFused = false>
 __global__ void __launch_bounds__(GemmCfg<BN, EPI>::kThreads, 1)
 gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
     const GemmParams p)
@@ -429,6 +454,42 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     tmem_ld_32x32(t_row + half * kColsPerWarp + c0, r0);
                     if (c0 + 32 < kColsPerWarp) tmem_ld_32x32(t_row + half * kColsPerWarp + c0 + 32, r1);
                     tmem_ld_wait();
+                    if constexpr (kFused) {
+                        // bias per column (the same for every row: broadcast loads), residual from this row
+                        int const col0 = b_row0 + half * kColsPerWarp + c0;
+                        auto fuse32 = [&](uint32_t (&r)[32], int col) {
+                            if (col >= p.rows_b) return;
+                            bool const has_bias = p.bias != nullptr;
+                            bool const has_res = p.residual != nullptr && a_row < p.rows_a;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint4 bw = make_uint4(0, 0, 0, 0), rw = make_uint4(0, 0, 0, 0);
+                                if (has_bias) bw = __ldg(reinterpret_cast<const uint4*>(p.bias + col + 8 * q));
+                                if (has_res)
+                                    rw = __ldg(reinterpret_cast<const uint4*>(
+                                        p.residual + static_cast<int64_t>(a_row) * p.ldo + col + 8 * q));
+                                uint32_t const bws[4] = {bw.x, bw.y, bw.z, bw.w};
+                                uint32_t const rws[4] = {rw.x, rw.y, rw.z, rw.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    float lo = epilogue_value(__uint_as_float(r[8 * q + 2 * i]),
+                                        bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] & 0xFFFFu))),
+                                        has_bias, p.act);
+                                    float hi = epilogue_value(__uint_as_float(r[8 * q + 2 * i + 1]),
+                                        bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] >> 16))),
+                                        has_bias, p.act);
+                                    if (has_res) {
+                                        lo += bf16_lo(rws[i]);
+                                        hi += bf16_hi(rws[i]);
+                                    }
+                                    r[8 * q + 2 * i] = __float_as_uint(lo);
+                                    r[8 * q + 2 * i + 1] = __float_as_uint(hi);
+                                }
+                            }
+                        };
+                        fuse32(r0, col0);
+                        if (c0 + 32 < kColsPerWarp) fuse32(r1, col0 + 32);
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         packed[c0 / 2 + j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
@@ -490,10 +551,17 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int j = 0; j < 16; ++j) {
                         int const m = b_row0 + c0 + j;
                         if (m < p.rows_b && a_row < p.rows_a) {
-                            if constexpr (EPI == EPI_BF16)
+                            if constexpr (EPI == EPI_BF16) {
+                                float v = __uint_as_float(r[j]);
+                                if constexpr (kFused) {
+                                    v = epilogue_value(v, p.bias != nullptr ? bias_term(p.bias[a_row]) : 0.f,
+                                        p.bias != nullptr, p.act);
+                                    if (p.residual != nullptr)
+                                        v += __bfloat162float(p.residual[static_cast<int64_t>(m) * p.ldo + a_row]);
+                                }
                                 static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row]
-                                    = __float2bfloat16_rn(__uint_as_float(r[j]));
-                            else
+                                    = __float2bfloat16_rn(v);
+                            } else
                                 p.ws[static_cast<int64_t>(c.split) * p.out_rows * p.ldo
                                     + static_cast<int64_t>(m) * p.ldo + a_row] = __uint_as_float(r[j]);
                         }
@@ -538,9 +606,16 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < BN; ++j) {
                 int const m = b_row0 + j;
-                if (m < p.rows_b && a_row < p.rows_a)
-                    static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row]
-                        = __float2bfloat16_rn(red_v[j]);
+                if (m < p.rows_b && a_row < p.rows_a) {
+                    float v = red_v[j];
+                    if constexpr (kFused) {
+                        v = epilogue_value(v, p.bias != nullptr ? bias_term(p.bias[a_row]) : 0.f, p.bias != nullptr,
+                            p.act);
+                        if (p.residual != nullptr)
+                            v += __bfloat162float(p.residual[static_cast<int64_t>(m) * p.ldo + a_row]);
+                    }
+                    static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row] = __float2bfloat16_rn(v);
+                }
             }
         }
     }
@@ -559,9 +634,11 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
-// Sums the split-K partials in slice order and rounds once to bf16. n % 4 == 0.
+// Sums the split-K partials in slice order, applies the dense epilogue when there is one (bias / act / residual all
+// absent: the plain sum) and rounds once to bf16. n % 4 == 0.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float4* __restrict__ ws, uint2* __restrict__ out,
-    int64_t quads, int splits)
+    int64_t quads, int splits, int n, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
+    int act)
 {
     griddep_launch_dependents();
     griddep_wait();                                       // the partials are the preceding kernel's output
@@ -574,6 +651,21 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float4* __rest
         acc.y += v.y;
         acc.z += v.z;
         acc.w += v.w;
+    }
+    if (bias != nullptr || residual != nullptr || act != 0) {
+        int const col = static_cast<int>((i * 4) % n);
+        bool const hb = bias != nullptr;
+        acc.x = epilogue_value(acc.x, hb ? bias_term(bias[col]) : 0.f, hb, act);
+        acc.y = epilogue_value(acc.y, hb ? bias_term(bias[col + 1]) : 0.f, hb, act);
+        acc.z = epilogue_value(acc.z, hb ? bias_term(bias[col + 2]) : 0.f, hb, act);
+        acc.w = epilogue_value(acc.w, hb ? bias_term(bias[col + 3]) : 0.f, hb, act);
+        if (residual != nullptr) {
+            uint2 const rw = *reinterpret_cast<const uint2*>(residual + i * 4);
+            acc.x += bf16_lo(rw.x);
+            acc.y += bf16_hi(rw.x);
+            acc.z += bf16_lo(rw.y);
+            acc.w += bf16_hi(rw.y);
+        }
     }
     uint2 o;
     o.x = pack_bf16x2(acc.x, acc.y);

@@ -160,13 +160,13 @@ inline int pdl_attribute(cudaLaunchAttribute* attr)
     return 1;
 }
 
-template <int BN, int EPI, bool kSwap, bool kGrouped>
+template <int BN, int EPI, bool kSwap, bool kGrouped, bool kFused = false>
 inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int grid,
     cudaStream_t stream)
 {
     using C = GemmCfg<BN, EPI>;
     static std::atomic<uint64_t> done{0};
-    auto kernel = gemm_mxf8_kernel<BN, EPI, kSwap, kGrouped>;
+    auto kernel = gemm_mxf8_kernel<BN, EPI, kSwap, kGrouped, kFused>;
     int const rc = ensure_smem_attr(kernel, C::kSmemBytes, done);
     if (rc != 0) return rc;
     if constexpr (kSwap) {
@@ -205,7 +205,7 @@ inline void cluster_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* 
 
 // How many clusters of `splits` CTAs of the cluster split-K kernel this device runs at the same time (one CTA per
 // SM, a cluster inside one GPC); asked once per device and cluster size. 0 = cannot be launched.
-template <int BN>
+template <int BN, bool kFused = false>
 inline int cluster_capacity(int splits)
 {
     using C = GemmCfg<BN, EPI_CLUSTER>;
@@ -215,7 +215,7 @@ inline int cluster_capacity(int splits)
     if (splits < 2 || splits > 8) return 0;
     int v = cap[dev][splits].load(std::memory_order_acquire);
     if (v == 0) {
-        auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false>;
+        auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false, kFused>;
         int clusters = 0;
         if (ensure_smem_attr(kernel, C::kSmemBytes, done) == 0) {
             cudaLaunchConfig_t cfg;
@@ -232,18 +232,21 @@ inline int cluster_capacity(int splits)
     return v - 1;
 }
 
-inline int cluster_capacity_bn(int bn, int splits)
+inline int cluster_capacity_bn(int bn, int splits, bool fused)
 {
+    if (fused)
+        return bn == 16 ? cluster_capacity<16, true>(splits) : bn == 32 ? cluster_capacity<32, true>(splits)
+            : bn == 64 ? cluster_capacity<64, true>(splits) : 0;
     return bn == 16 ? cluster_capacity<16>(splits) : bn == 32 ? cluster_capacity<32>(splits)
         : bn == 64 ? cluster_capacity<64>(splits) : 0;
 }
 
 // The swapped kernel with split-K inside thread-block clusters of `splits` CTAs (one CTA per work item).
-template <int BN>
+template <int BN, bool kFused = false>
 inline int launch_gemm_cluster(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int items,
     cudaStream_t stream)
 {
-    auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false>;
+    auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false, kFused>;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     cluster_launch_config<BN>(cfg, attr, items, p.splits, stream);
@@ -337,8 +340,16 @@ inline bool splitk_through_workspace()
 }
 
 // D[M, N] = A[M, K] * W[N, K]^T.
+// The dense epilogue of one call: out = bf16(act(acc + bias[n]) + residual[m, n]); all absent = the plain GEMM.
+struct DenseEpi {
+    const void* bias = nullptr;
+    const void* residual = nullptr;
+    int act = 0;
+    bool any() const { return bias != nullptr || residual != nullptr || act != 0; }
+};
+
 inline int launch_dense(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
-    int64_t k, void* ws, int64_t ws_bytes, cudaStream_t stream)
+    int64_t k, void* ws, int64_t ws_bytes, cudaStream_t stream, DenseEpi epi = DenseEpi{})
 {
     int const sms = sm_count();
     DensePlan const pl = plan_dense(m, n, k, sms);
@@ -348,7 +359,8 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
             static_cast<long long>(ws_bytes));
         return FSO_ERR_INVALID;
     }
-    if (use_pair_kernel(m, n, sms, pl.swap, pl.splits)) return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
+    bool const fused = epi.any();
+    if (!fused && use_pair_kernel(m, n, sms, pl.swap, pl.splits)) return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
     CUtensorMap ta, tb;
     GemmParams p{};
     p.kb_total = static_cast<int>(k / 128);
@@ -362,6 +374,9 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     p.ws = static_cast<float*>(ws);
     p.out_rows = m;
     p.out_align32 = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 ? 1 : 0;
+    p.bias = static_cast<const __nv_bfloat16*>(epi.bias);
+    p.residual = static_cast<const __nv_bfloat16*>(epi.residual);
+    p.act = epi.act;
     int rc;
     if (pl.swap) {
         if ((rc = make_operand_map(&ta, w, n, k, 128)) != 0) return rc;
@@ -386,7 +401,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
         for (int s2 = pl.splits; s2 >= 2; --s2) {
             int const per = (p.kb_total + s2 - 1) / s2;
             if ((p.kb_total + per - 1) / per != s2) continue;
-            if (cluster_capacity_bn(pl.bn, s2) >= pl.tiles_a) {
+            if (cluster_capacity_bn(pl.bn, s2, fused) >= pl.tiles_a) {
                 if (s2 == pl.splits || pl.tiles_a * s2 * 2 >= sms) {
                     splits = s2;
                     in_cluster = true;
@@ -401,6 +416,10 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     int const slots = pl.swap ? 2 * sms : sms;          // the swapped kernels run two CTAs per SM
     int const grid = static_cast<int>(items < slots ? items : slots);
     if (in_cluster && !splitk_through_workspace()) {
+        if (fused)
+            return pl.bn == 16 ? launch_gemm_cluster<16, true>(ta, tb, p, static_cast<int>(items), stream)
+                : pl.bn == 32 ? launch_gemm_cluster<32, true>(ta, tb, p, static_cast<int>(items), stream)
+                              : launch_gemm_cluster<64, true>(ta, tb, p, static_cast<int>(items), stream);
         return pl.bn == 16 ? launch_gemm_cluster<16>(ta, tb, p, static_cast<int>(items), stream)
             : pl.bn == 32 ? launch_gemm_cluster<32>(ta, tb, p, static_cast<int>(items), stream)
                           : launch_gemm_cluster<64>(ta, tb, p, static_cast<int>(items), stream);
@@ -409,6 +428,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
 #define FSO_DENSE_CASE(BN_, SWAP_)                                                                                 \
     if (pl.bn == BN_ && pl.swap == SWAP_) {                                                                        \
         rc = partial ? launch_gemm_inst<BN_, EPI_PARTIAL, SWAP_, false>(ta, tb, p, grid, stream)                   \
+            : fused  ? launch_gemm_inst<BN_, EPI_BF16, SWAP_, false, true>(ta, tb, p, grid, stream)                \
                      : launch_gemm_inst<BN_, EPI_BF16, SWAP_, false>(ta, tb, p, grid, stream);                     \
     } else
     FSO_DENSE_CASE(16, true)
@@ -432,7 +452,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
         cfg.attrs = attr;
         cfg.numAttrs = pl.swap ? pdl_attribute(&attr[0]) : 0;
         FSO_CUDA(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float4*>(ws), static_cast<uint2*>(d),
-            quads, splits));
+            quads, splits, static_cast<int>(n), p.bias, p.residual, p.act));
         rc = launch_status("splitk_reduce_kernel");
     }
     return rc;

@@ -157,6 +157,29 @@ int fso_gemm_mxfp8(const void* a, const void* sfa, const void* w, const void* sf
     return launch_dense(a, sfa, w, sfw, d, m, n, k, ws, ws_bytes, as_stream(stream));
 }
 
+int fso_gemm_mxfp8_epilogue(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m,
+    int64_t n, int64_t k, const void* bias, const void* residual, int64_t activation, void* ws, int64_t ws_bytes,
+    void* stream)
+{
+    int const rc = check_gemm_shape("fso_gemm_mxfp8_epilogue", m, n, k);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(activation == 0 || activation == 1,
+        "fso_gemm_mxfp8_epilogue: activation must be 0 (identity) or 1 (erf-GELU), got %lld",
+        static_cast<long long>(activation));
+    if (m == 0) return 0;
+    FSO_REQUIRE(a && sfa && w && sfw && d, "fso_gemm_mxfp8_epilogue: NULL pointer");
+    FSO_REQUIRE(aligned16(a) && aligned16(sfa) && aligned16(w) && aligned16(sfw) && aligned16(d),
+        "fso_gemm_mxfp8_epilogue: every operand must be 16-byte aligned (TMA reads them in place)");
+    FSO_REQUIRE(ws == nullptr || aligned16(ws), "fso_gemm_mxfp8_epilogue: the workspace must be 16-byte aligned");
+    FSO_REQUIRE((bias == nullptr || aligned16(bias)) && (residual == nullptr || aligned16(residual)),
+        "fso_gemm_mxfp8_epilogue: bias and residual must be 16-byte aligned");
+    DenseEpi epi;
+    epi.bias = bias;
+    epi.residual = residual;
+    epi.act = static_cast<int>(activation);
+    return launch_dense(a, sfa, w, sfw, d, m, n, k, ws, ws_bytes, as_stream(stream), epi);
+}
+
 int fso_moe_plan_make(int64_t tokens, int64_t topk, int64_t num_experts, fso_moe_plan* plan)
 {
     FSO_REQUIRE(plan != nullptr, "fso_moe_plan_make: plan is NULL");

@@ -61,8 +61,8 @@ def describe() -> str:
         "fused kernel (value = bf16(fp8 * scale), then the 1x32 rule); a bf16 weight is quantized to MXFP8 directly.",
         "linear(): the 1x32 activation quantizer, then one tcgen05 block-scaled GEMM kernel family (activation rows "
         "on MMA-M for M > 64, weight rows on MMA-M for M <= 64, split-K with an ordered reduce where the tile count "
-        "leaves SMs idle). bias / residual / activation are validated and refused (NotImplementedError); "
-        "linear_quantized runs linear followed by the activation quantizer.",
+        "leaves SMs idle). bias / residual / activation 'gelu_erf' are applied to the fp32 accumulator before the one "
+        "rounding; linear_quantized runs linear (bias, activation) followed by the activation quantizer.",
     ]
     if arch // 10 != SERVED_MAJOR:
         lines.append(f"This device ({arch_label(arch)}) serves no format.")
@@ -360,10 +360,15 @@ def _x_bf16_storage(x):
     return x
 
 
-def _refuse_epilogue(op: str):
-    raise NotImplementedError(
-        f"{op}: the dense epilogue (bias / residual / activation) is validated but not applied by this build's GEMM "
-        f"yet; call without it and apply it to the bf16 result")
+def _epilogue_storage(op: str, bias, residual):
+    """The epilogue kernels read bias and residual with 16-byte loads: a bias off a 16-byte boundary is cloned (it is
+    N elements); a residual off one is refused, as in the reference (a copy of [M, N] is the caller's call)."""
+    if bias is not None and bias.numel() > 0 and bias.data_ptr() % 16 != 0:
+        bias = bias.clone()
+    if residual is not None and residual.numel() > 0 and residual.data_ptr() % 16 != 0:
+        raise NotImplementedError(f"{op}: the residual's data pointer is {residual.data_ptr() % 16} bytes past a "
+                                  f"16-byte boundary; the epilogue reads its rows with 16-byte loads")
+    return bias, residual
 
 
 # ------------------------------------------------------------------------------------------------ custom ops
@@ -391,11 +396,10 @@ def _dense_linear_op(x, weight, scale, kind, bias=None, x_scale=None, residual=N
         x = _x_bf16_storage(x)
     if m == 0:
         return x.new_empty((0, n), dtype=torch.bfloat16)
-    if has_epi:
-        _refuse_epilogue(op)
+    bias, residual = _epilogue_storage(op, bias, residual)
     if x_scale is None:
         x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
-    return _ops.linear_mxfp8(x, weight, x_scale, scale)
+    return _ops.linear_mxfp8(x, weight, x_scale, scale, bias, residual, 1 if activation == "gelu_erf" else 0)
 
 
 @_dense_linear_op.register_fake
@@ -430,11 +434,10 @@ def _dense_linear_quantized_op(x, weight, scale, kind, bias=None, x_scale=None, 
         x = _x_bf16_storage(x)
     if m == 0:
         return (x.new_empty((0, n), dtype=FP8), _empty_act_scale(0, n, x.device))
-    if has_epi:
-        _refuse_epilogue(op)
+    bias, _ = _epilogue_storage(op, bias, None)
     if x_scale is None:
         x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
-    y = _ops.linear_mxfp8(x, weight, x_scale, scale)
+    y = _ops.linear_mxfp8(x, weight, x_scale, scale, bias, None, 1 if activation == "gelu_erf" else 0)
     return _ops.quantize_1x32_fp8(y, activation=True)
 
 

@@ -79,6 +79,16 @@ int fso_gemm_mxfp8_ws_bytes(int64_t m, int64_t n, int64_t k, int64_t* bytes);
 int fso_gemm_mxfp8(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
                    int64_t k, void* ws, int64_t ws_bytes, void* stream);
 
+/* fso_gemm_mxfp8 with the dense epilogue applied to the fp32 accumulator (after any split-K sum) before the one
+ * rounding: d = bf16( act(acc + bias[n]) + residual[m, n] ). bias bf16 [N] (a +0.0 bias element counts as -0.0, so
+ * that a zero bias gives the bytes of no bias), residual bf16 [M, N], either may be NULL; activation 0 = identity,
+ * 1 = erf-GELU 0.5 v (1 + erf(v / sqrt 2)) in fp32. With all three absent the call is fso_gemm_mxfp8.
+ * Replaces: the DenseEpilogue argument of linear_mxfp8_raw, csrc/gemm/include/blockscale_gemm/common/epilogue.cuh:1-30
+ * (python/fish_scales_ops/gemm/_epilogue.py:1-30). */
+int fso_gemm_mxfp8_epilogue(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m,
+                            int64_t n, int64_t k, const void* bias, const void* residual, int64_t activation,
+                            void* ws, int64_t ws_bytes, void* stream);
+
 /* Host-static sizes of one MoE layer call (functions of the argument shapes only).
  * Replaces: _mxfp8_layer_plan / moe_compact_num_blocks, python/fish_scales_ops/gemm/mxfp8.py:1653-1728, 1228-1239. */
 typedef struct fso_moe_plan {

@@ -223,6 +223,24 @@ def dense_linear(x, w_q, w_sf) -> torch.Tensor:
     return xd @ wd.t()
 
 
+def dense_epilogue(acc: torch.Tensor, bias=None, residual=None, activation=None) -> torch.Tensor:
+    """The dense epilogue on an fp32 accumulator (csrc/gemm/include/blockscale_gemm/common/epilogue.cuh:1-30 of the
+    reference): v = acc + bias[n] (a +0.0 bias counts as -0.0); v = erf-GELU(v) = 0.5 v (1 + erf(v * fp32(1/sqrt 2)))
+    when asked; v += residual[m, n]. fp32 throughout, not rounded (the caller compares within the output tolerance)."""
+    v = acc.to(torch.float32).clone()
+    if bias is not None:
+        b = bias.detach().cpu().to(torch.float32)
+        b = torch.where(b == 0, torch.full_like(b, -0.0), b)
+        v = v + b
+    if activation == "gelu_erf":
+        v = 0.5 * v * (1.0 + torch.erf(v * np.float32(0.70710678118654752440)))
+    elif activation is not None:
+        raise ValueError(activation)
+    if residual is not None:
+        v = v + residual.detach().cpu().to(torch.float32)
+    return v
+
+
 def moe_layer(hidden, w13_q, w13_sf, w2_q, w2_sf, topk_ids, topk_w, interleaved: bool = True) -> torch.Tensor:
     """fp32 MoE layer on quantized operands, modelling both quantization points (the gathered activation and the
     fp32 silu(gate)*up intermediate requantized with the 1x32 rule before FC2); ids outside [0, E) are skipped.

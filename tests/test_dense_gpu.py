@@ -133,8 +133,12 @@ def test_refusals_before_launch(fso, device_ok):
         fso.dense.linear(x, weight, x_scale=sx)
     with pytest.raises(ValueError):
         fso.dense.linear(xq, weight, x_scale=sx[:-1])
-    with pytest.raises(NotImplementedError):
-        fso.dense.linear(x, weight, bias=torch.zeros(256, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        fso.dense.linear(x, weight, bias=torch.zeros(255, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        fso.dense.linear(x, weight, bias=torch.zeros(256, dtype=torch.float32, device="cuda"))
+    with pytest.raises(ValueError):
+        fso.dense.linear(x, weight, residual=torch.zeros(8, 128, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(ValueError):
         fso.dense.linear(x, weight, activation="nope")
     with pytest.raises(NotImplementedError):
@@ -345,3 +349,52 @@ def test_dependent_launch_chain_equals_plain_launches(fso, device_ok):
     for m in got["1"]:
         for a, b in zip(got["1"][m], got["0"][m]):
             assert torch.equal(a, b), m
+
+
+# (M, N, K): the normal kernel with 128- and 256-wide tiles and a ragged M, its split-K (epilogue in the reduce
+# kernel), the swapped kernel without split, with the cluster split-K and with the workspace split-K of a long K
+EPI_SHAPES = [(200, 384, 640), (300, 1024, 1024), (1024, 4096, 512), (128, 256, 8192), (16, 28672, 256),
+              (16, 4096, 4096), (40, 512, 1536), (4, 256, 16384)]
+
+
+@pytest.mark.parametrize("m,n,k", EPI_SHAPES)
+def test_dense_epilogue_bias_gelu_residual(fso, oracle, device_ok, m, n, k):
+    """out = bf16(act(acc + bias[n]) + residual[m, n]) with one rounding
+    (csrc/gemm/include/blockscale_gemm/common/epilogue.cuh:1-30 of the reference), every combination of the three
+    fields, against the oracle's fp32 statement within the output tolerance."""
+    x, w = inputs.activation(m, k, m + k), inputs.weight(n, k, n + k)
+    weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
+    g = inputs.gen(m * n)
+    bias = torch.randn(n, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    res = torch.randn(m, n, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    acc = _oracle_out(oracle, x, inputs.to_np_u8(weight.weight), inputs.to_np_u32(weight.scale))
+    plain = fso.dense.linear(x.cuda(), weight)
+    for use_bias, use_res, act in ((1, 0, None), (0, 1, None), (0, 0, "gelu_erf"), (1, 1, "gelu_erf"), (1, 1, None)):
+        y = fso.dense.linear(x.cuda(), weight, bias=bias.cuda() if use_bias else None,
+                             residual=res.cuda() if use_res else None, activation=act)
+        ref = oracle.dense_epilogue(acc, bias if use_bias else None, res if use_res else None, act)
+        inputs.assert_close_to_oracle(y, ref, f"M={m} N={n} K={k} bias={use_bias} res={use_res} act={act}")
+    # a zero bias (of either sign) and a zero residual leave the bytes of the plain call
+    zb = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    assert torch.equal(fso.dense.linear(x.cuda(), weight, bias=zb), plain)
+    assert torch.equal(fso.dense.linear(x.cuda(), weight, bias=-zb), plain)
+    # linear_quantized = quantize(linear(bias, activation))
+    yq, ys = fso.dense.linear_quantized(x.cuda(), weight, bias=bias.cuda(), activation="gelu_erf")
+    want_q, want_s = fso.dense.quantize_activation(fso.dense.linear(x.cuda(), weight, bias=bias.cuda(),
+                                                                    activation="gelu_erf"))
+    assert torch.equal(yq.view(torch.uint8), want_q.view(torch.uint8)) and torch.equal(ys, want_s)
+
+
+def test_dense_epilogue_against_torch_on_device(fso, device_ok):
+    """The same epilogue written with torch ops on the fp32 result of the plain call's operands: erf-GELU and the
+    additions in fp32, one rounding."""
+    m, n, k = 256, 512, 1024
+    x, w = inputs.activation(m, k, 1).cuda(), inputs.weight(n, k, 2).cuda()
+    weight = fso.dense.prepare_weight(w, format="mxfp8")
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16)
+    res = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+    y = fso.dense.linear(x, weight, bias=bias, residual=res, activation="gelu_erf")
+    base = fso.dense.linear(x, weight).float()               # bf16-rounded accumulator: close enough for a bound
+    want = torch.nn.functional.gelu(base + bias.float()) + res.float()
+    err = (y.float() - want).abs().max() / want.abs().max()
+    assert float(err) < 2e-2
