@@ -35,6 +35,7 @@ SIGNATURES = {
                                 _c_p],
     "fso_quantize_activation_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_p],
     "fso_stream_fence": [_c_p],
+    "fso_silu_mul_quantize_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_p],
     "fso_moe_topk_from_logits": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p,
                                  _c_p],
     "fso_ep_plan_count": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p],

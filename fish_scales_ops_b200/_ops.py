@@ -46,6 +46,19 @@ def quantize_1x32_fp8(x: torch.Tensor, interleave_i: int = 0, activation: bool =
     return xq, sf
 
 
+def silu_mul_quantize_1x32_fp8(gu: torch.Tensor):
+    """bf16 [M, 2I] (gate | up) -> (float8_e4m3fn [M, I], int32 scale words): silu(gate) * up, quantized."""
+    m, two_i = int(gu.shape[0]), int(gu.shape[1])
+    inter = two_i // 2
+    with torch.cuda.device(gu.device):
+        xq = torch.empty((m, inter), dtype=FP8, device=gu.device)
+        sf = torch.empty((sf_words(m, inter),), dtype=torch.int32, device=gu.device)
+        if m > 0:
+            check(lib().fso_silu_mul_quantize_1x32(ptr(gu), ptr(xq), ptr(sf), m, inter, stream_ptr()),
+                  "fso_silu_mul_quantize_1x32")
+    return xq, sf
+
+
 def stream_fence(device) -> None:
     """One empty plain launch on the current stream of ``device`` (orders programmatic dependent launches)."""
     with torch.cuda.device(device):

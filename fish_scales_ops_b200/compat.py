@@ -9,7 +9,7 @@ import torch
 from . import _ops
 from ._arch import SERVED_MAJOR, arch_label, device_arch
 
-__all__ = ["moe_topk_from_logits", "moe_router_topk"]
+__all__ = ["moe_topk_from_logits", "moe_router_topk", "silu_chunk_mul_quantize_1x32_fp8"]
 
 _MAX_EXPERTS = 1024
 _MAX_TOPK = 8
@@ -84,3 +84,40 @@ def moe_router_topk(hidden: torch.Tensor, router_weight: torch.Tensor, topk: int
     logits = torch.nn.functional.linear(hidden, router_weight)
     return moe_topk_from_logits(logits, topk, renormalize=renormalize, with_shared_gate=with_shared_gate,
                                 num_token_non_padded=num_token_non_padded, expert_map=expert_map)
+
+
+@torch.library.custom_op(
+    "fish_scales_ops::silu_chunk_mul_quantize_1x32",
+    mutates_args=(),
+    schema="(Tensor gu, bool use_ue8m0=True) -> (Tensor, Tensor)",
+)
+def _silu_chunk_mul_quantize_op(gu, use_ue8m0=True):
+    op = f"fish_scales_ops::silu_chunk_mul_quantize_1x32 ({arch_label(device_arch())})"
+    if not gu.is_cuda or gu.dtype != torch.bfloat16 or gu.dim() != 2:
+        raise ValueError(f"{op}: gu must be a CUDA bf16 [M, 2*INTER] tensor, got {gu.dtype} {tuple(gu.shape)}")
+    if int(gu.shape[1]) % 256 != 0:
+        raise ValueError(f"{op}: INTER = {int(gu.shape[1]) / 2:g} must be a multiple of 128")
+    if not use_ue8m0:
+        raise NotImplementedError(f"{op}: only the UE8M0 (MXFP8) scale form is served")
+    if device_arch() // 10 != SERVED_MAJOR:
+        raise NotImplementedError(f"{op}: this build serves sm_100-family devices")
+    if not gu.is_contiguous() or gu.data_ptr() % 32 != 0:
+        gu = gu.contiguous() if not gu.is_contiguous() else gu.clone()
+    return _ops.silu_mul_quantize_1x32_fp8(gu)
+
+
+@_silu_chunk_mul_quantize_op.register_fake
+def _silu_chunk_mul_quantize_fake(gu, use_ue8m0=True):
+    m, inter = gu.shape[0], gu.shape[1] // 2
+    return (gu.new_empty((m, inter), dtype=torch.float8_e4m3fn),
+            gu.new_empty(((m + 127) // 128 * 128 * (inter // 128),), dtype=torch.int32))
+
+
+def silu_chunk_mul_quantize_1x32_fp8(gu: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The step between the gate_up and the down projection of a SwiGLU MLP
+    (python/fish_scales_ops/gemm/mxfp8.py:216-236): ``gu`` bf16 ``[..., 2*INTER]`` with the gate in the first INTER
+    columns and up in the second; returns ``silu(gate) * up`` as ``(float8_e4m3fn [M, INTER], int32 scale words)`` in
+    the activation contract, ready for ``fso.dense.linear(xq, weight, x_scale=sx)``, without the product ever
+    reaching memory."""
+    two_i = int(gu.shape[-1])
+    return torch.ops.fish_scales_ops.silu_chunk_mul_quantize_1x32(gu.reshape(-1, two_i), True)

@@ -91,6 +91,17 @@ int fso_quantize_activation_1x32(const void* x, void* xq, void* sf, int64_t m, i
     return launch_quantize_1x32(x, xq, sf, m, k, 0, as_stream(stream), true);
 }
 
+int fso_silu_mul_quantize_1x32(const void* gu, void* xq, void* sf, int64_t m, int64_t inter, void* stream)
+{
+    FSO_REQUIRE(m >= 0 && inter > 0 && inter % 128 == 0,
+        "fso_silu_mul_quantize_1x32: INTER = %lld must be a positive multiple of 128", static_cast<long long>(inter));
+    if (m == 0) return 0;
+    FSO_REQUIRE(gu && xq && sf, "fso_silu_mul_quantize_1x32: NULL pointer");
+    FSO_REQUIRE((reinterpret_cast<uintptr_t>(gu) & 31u) == 0 && aligned16(xq) && (reinterpret_cast<uintptr_t>(sf) & 3u) == 0,
+        "fso_silu_mul_quantize_1x32: gu must be 32-byte aligned, xq 16-byte aligned and sf 4-byte aligned");
+    return launch_silu_mul_quantize(gu, xq, sf, m, inter, as_stream(stream));
+}
+
 __global__ void stream_fence_kernel() {}
 
 int fso_stream_fence(void* stream)

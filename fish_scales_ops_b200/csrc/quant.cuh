@@ -282,6 +282,86 @@ inline int launch_quantize_1x32(const void* x, void* q, void* sf, int64_t m, int
     return launch_status("fso_quantize_1x32");
 }
 
+// ------------------------------------------------------------------------------------------- SiLU(gate) * up -> MXFP8
+
+// gu bf16 [M, 2I]: columns [0, I) are the gate, [I, 2I) the up projection. h = silu(gate) * up in fp32 (hardware
+// tanh approximation: silu(g) = 0.5 g (1 + tanh(0.5 g))), quantized with the 1x32 rule without h ever reaching
+// memory. 16 outputs per thread (two 256-bit loads, one 128-bit store), 2 lanes per 1x32 block, 8 per scale word.
+// Rows in [m, m_pad) only get their zero scale words.
+__global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const uint8_t* __restrict__ gu, uint4* __restrict__ q,
+    uint32_t* __restrict__ sf, uint32_t m, uint32_t m_pad, uint32_t kb)
+{
+    griddep_launch_dependents();      // the down projection launched behind this kernel may start loading weights
+    griddep_wait();                   // gu is the gate_up projection's output
+    uint32_t const sub = threadIdx.x & 7;
+    uint32_t const c = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;        // chunk (row, kp) of the output
+    if (c >= m_pad * kb) return;                                            // whole groups of 8 lanes leave together
+    uint32_t const row = c / kb;
+    uint32_t const kp = c - row * kb;
+    bool const live = row < m;
+    uint32_t g[8], u[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = u[i] = 0;
+    if (live) {
+        const uint8_t* const src = gu + (static_cast<size_t>(row) * (2 * kb) + kp) * 256 + sub * 32;
+        ld_nc_256(src, g);
+        ld_nc_256(src + static_cast<size_t>(kb) * 256, u);
+    }
+    float h[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float const g0 = __uint_as_float(g[i] << 16), g1 = __uint_as_float(g[i] & 0xFFFF0000u);
+        float const u0 = __uint_as_float(u[i] << 16), u1 = __uint_as_float(u[i] & 0xFFFF0000u);
+        float t0, t1;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(0.5f * g0));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(0.5f * g1));
+        h[2 * i] = (0.5f * g0) * (1.f + t0) * u0;
+        h[2 * i + 1] = (0.5f * g1) * (1.f + t1) * u1;
+        amax = fmaxf(amax, fmaxf(fabsf(h[2 * i]), fabsf(h[2 * i + 1])));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, 1e-10f);
+    float qs;
+    uint32_t const byte = e8m0_from_amax(amax, qs);
+    uint32_t const word = word_from_8lanes(byte, sub);
+    if (live) {
+        uint4 o;
+        o.x = fp8x4(__fmul_rn(h[0], qs), __fmul_rn(h[1], qs), __fmul_rn(h[2], qs), __fmul_rn(h[3], qs));
+        o.y = fp8x4(__fmul_rn(h[4], qs), __fmul_rn(h[5], qs), __fmul_rn(h[6], qs), __fmul_rn(h[7], qs));
+        o.z = fp8x4(__fmul_rn(h[8], qs), __fmul_rn(h[9], qs), __fmul_rn(h[10], qs), __fmul_rn(h[11], qs));
+        o.w = fp8x4(__fmul_rn(h[12], qs), __fmul_rn(h[13], qs), __fmul_rn(h[14], qs), __fmul_rn(h[15], qs));
+        q[(static_cast<size_t>(row) * kb + kp) * 8 + sub] = o;
+    }
+    if (sub == 0) sf[sf_word_index(row, kp, kb)] = live ? word : 0u;
+}
+
+inline int launch_silu_mul_quantize(const void* gu, void* q, void* sf, int64_t m, int64_t inter, cudaStream_t stream)
+{
+    int64_t const m_pad = (m + 127) / 128 * 128;
+    int const kb = static_cast<int>(inter / 128);
+    if (m_pad * kb >= (1ll << 28)) {
+        set_error("fso_silu_mul_quantize_1x32: %lld x %lld is beyond the kernel's index range; split the call by rows",
+            static_cast<long long>(m), static_cast<long long>(inter));
+        return FSO_ERR_INVALID;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>((m_pad * kb * 8 + 255) / 256), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (quantizer_pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
+    FSO_CUDA(cudaLaunchKernelEx(&cfg, silu_mul_quantize_kernel, static_cast<const uint8_t*>(gu), static_cast<uint4*>(q),
+        static_cast<uint32_t*>(sf), static_cast<uint32_t>(m), static_cast<uint32_t>(m_pad), static_cast<uint32_t>(kb)));
+    return launch_status("silu_mul_quantize_kernel");
+}
+
 // ---------------------------------------------------------------------------------------------------- block-FP8 -> MXFP8
 
 // 16 e4m3 codes per thread (one 16-byte load); 2 lanes per 32-element block, 8 lanes per 128-element chunk.

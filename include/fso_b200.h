@@ -56,6 +56,14 @@ int fso_quantize_activation_1x32(const void* x, void* xq, void* sf, int64_t m, i
  * Replaces: _complete_handle, python/fish_scales_ops/dense/__init__.py:605-620. */
 int fso_stream_fence(void* stream);
 
+/* The step between the gate_up and the down projection of a SwiGLU MLP: gu bf16 [M, 2*INTER] (columns [0, INTER)
+ * gate, [INTER, 2*INTER) up) -> h = silu(gate) * up quantized with the 1x32 rule, xq e4m3 [M, INTER] and sf in the
+ * layout of fso_quantize_1x32, without h reaching memory. silu uses the hardware tanh approximation, so the bytes
+ * are defined up to that approximation (output tolerance). Launched with programmatic dependent launch like the
+ * activation quantizer. gu 32-byte aligned. Replaces: silu_chunk_mul_quantize_1x32,
+ * python/fish_scales_ops/gemm/mxfp8.py:216-236 (csrc/gemm/ops/quant_kernels.cu:690-727). */
+int fso_silu_mul_quantize_1x32(const void* gu, void* xq, void* sf, int64_t m, int64_t inter, void* stream);
+
 /* Block-FP8 checkpoint (e4m3 [N, K] + one fp32 scale per 128x128 tile, [N/128, K/128]) -> MXFP8: each value is
  * bf16_rne(float(fp8) * scale) and then goes through the 1x32 rule. N % 128 == 0. interleave_i as in
  * fso_quantize_1x32 (stacked experts, I % 128 == 0; the tile scale follows the source row).
