@@ -4,6 +4,7 @@
 #include <atomic>
 #include <mutex>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -101,6 +102,24 @@ inline void pick_splits(int64_t tiles, int kb, int sms, int min_kb, int max_s, i
     *kb_per = (kb + best_s - 1) / best_s;
 }
 
+// Decode-sized (swapped) problems are latency-bound, not wave-bound: measured on the four Llama-3-8B shapes at M = 16,
+// about 128-200 half-SM CTAs is the best grid (gate_up: 224 tiles unsplit; qkv 48 x 4; o_proj and down 32 x 4; eight
+// slices of the same shapes are slower again). So: the largest slice count that keeps tiles * slices <= 200, at
+// most 4 once the tiles alone fill a sixth of the slots, every slice at least 4 K blocks and none empty.
+inline void pick_decode_splits(int64_t tiles, int kb, int limit, int* splits, int* kb_per)
+{
+    int best = 1;
+    int const smax = tiles >= 25 ? (limit < 4 ? limit : 4) : limit;
+    for (int s = 2; s <= smax; ++s) {
+        int const per = (kb + s - 1) / s;
+        if (per < 4) break;
+        if ((kb + per - 1) / per != s) continue;
+        if (tiles * s <= 200) best = s;
+    }
+    *splits = best;
+    *kb_per = (kb + best - 1) / best;
+}
+
 inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
 {
     DensePlan p{};
@@ -111,7 +130,7 @@ inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
         p.tiles_a = static_cast<int>(n / 128);
         p.tiles_b = 1;
         p.group_a = p.tiles_a;
-        pick_splits(p.tiles_a, kb, sms, 4, cluster_split_limit(p.bn), &p.splits, &p.kb_per_split);
+        pick_decode_splits(p.tiles_a, kb, cluster_split_limit(p.bn), &p.splits, &p.kb_per_split);
     } else {
         p.swap = false;
         int const tiles_m = static_cast<int>((m + 127) / 128);
@@ -401,7 +420,8 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
         for (int s2 = pl.splits; s2 >= 2; --s2) {
             int const per = (p.kb_total + s2 - 1) / s2;
             if ((p.kb_total + per - 1) / per != s2) continue;
-            if (cluster_capacity_bn(pl.bn, s2, fused) >= pl.tiles_a) {
+            // the occupancy query counts one CTA of a cluster per SM; two of these half-SM CTAs share one
+            if (2 * cluster_capacity_bn(pl.bn, s2, fused) >= pl.tiles_a) {
                 if (s2 == pl.splits || pl.tiles_a * s2 * 2 >= sms) {
                     splits = s2;
                     in_cluster = true;
