@@ -542,7 +542,7 @@ def decode_ours(args):
     line = base_line(args, d, "dense_decode_weight_stream_gbs", "GB/s", worst["gemm_gbs"], total_us / 1e3, "strong",
                      "fp8_e4m3", {"workload": f"llama3-8b dense linears at M={m}, CUDA-graph replay, cold weights",
                                   "cells": cells, "l2": "rotated weight copies of at least 2 x L2 per shape"})
-    line["roofline"] = {"bound": "hbm", "kernel": "gemm_mxf8_kernel<16, swapped> (+ split-K reduce)",
+    line["roofline"] = {"bound": "hbm", "kernel": "gemm_mxf8_kernel<16, swapped> (split-K inside clusters)",
                         "achieved": worst["gemm_gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
                         "frac": worst["gemm_gbs"] / pk["hbm_gbs"], "traffic": None,
                         "peak_source": f"{pk['source']} copy bandwidth"}
