@@ -9,7 +9,9 @@ Workloads (``--workload``):
             tcgen05 block-scaled GEMM) over the Llama-3-8B gate_up projection, M=8192, N=28672, K=4096. Operands and
             output exceed L2, so every step streams them from HBM. With N > 1 (torch.distributed.run, one rank per
             GPU) the weight rows are split N ways (column parallel, no data-path collective); ``value`` is the whole
-            job's 2*M*N*K over the slowest rank's device time.
+            job's 2*M*N*K over the slowest rank's device time. Unless ``--no-moe`` is given, the same run then
+            measures the ``moe`` workload below with fewer steps and attaches it as the line's ``"moe"`` object
+            (the second half of the headline metric: MoE layer tokens/s at 1/2/4/8 GPUs).
   moe       one DeepSeek-V3-shaped MoE layer (256 experts, top-8, H=7168, I=2048), 4096 tokens per GPU, experts
             sharded 256/N per GPU, token rows exchanged by the library's kernels over peer memory (weak scaling;
             ``FSO_B200_EP_TRANSPORT=collective`` uses NCCL all-to-all-v instead); ``--moe-config mixtral``
@@ -111,6 +113,7 @@ class Dist:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (B200); this arm has no CPU path")
         torch.cuda.set_device(self.local)
+        self.keep = False
         if self.world > 1:
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
 
@@ -126,9 +129,23 @@ class Dist:
         return [float(v) for v in t.tolist()]
 
     def close(self):
+        """Ends the process group, unless another workload of this run still needs it (``keep``)."""
+        if self.keep:
+            return
         if self.world > 1:
             self.dist.barrier()
             self.dist.destroy_process_group()
+
+
+_SHARED_DIST = None
+
+
+def shared_dist(torch) -> "Dist":
+    """One process group per run: the default run measures two workloads one after the other."""
+    global _SHARED_DIST
+    if _SHARED_DIST is None:
+        _SHARED_DIST = Dist(torch)
+    return _SHARED_DIST
 
 
 def timed_steps(torch, d: Dist, step, steps: int, warmup: int, per_step_events: bool = False):
@@ -235,7 +252,7 @@ def dense_ours(args):
     import fish_scales_ops_b200 as fso
     from fish_scales_ops_b200 import _ops, parallel
 
-    d = Dist(torch)
+    d = shared_dist(torch)
     m, n, k = dense_shape(args)
     r0, r1 = parallel.column_shard(n, d.world, d.rank)
     n_local = r1 - r0
@@ -398,7 +415,7 @@ def moe_ours(args):
     import fish_scales_ops_b200 as fso
     from fish_scales_ops_b200 import _ops, parallel
 
-    d = Dist(torch)
+    d = shared_dist(torch)
     cfg = MOE_CONFIGS[args.moe_config]
     if d.world > 1 and args.moe_config != "dsv3":
         raise SystemExit("the multi-GPU MoE workload is the DeepSeek-V3 config (expert parallel)")
@@ -516,7 +533,7 @@ def decode_ours(args):
     import fish_scales_ops_b200 as fso
     from fish_scales_ops_b200 import _ops
 
-    d = Dist(torch)
+    d = shared_dist(torch)
     fso.build()
     m = args.decode_m
     pk = peaks()
@@ -559,7 +576,7 @@ def quantize_ours(args):
     import fish_scales_ops_b200 as fso
     from fish_scales_ops_b200 import _ops
 
-    d = Dist(torch)
+    d = shared_dist(torch)
     fso.build()
     m, k = 8192, 4096
     x = dense_inputs(torch, m, 128, k)[0].cuda()
@@ -597,14 +614,35 @@ def main():
     ap.add_argument("--decode-m", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--shape", default=None, help="dense workload: M,N,K override (profiling on a smaller case)")
+    ap.add_argument("--no-moe", action="store_true",
+                    help="dense workload: do not also measure the DeepSeek-V3 MoE layer (the line's \"moe\" object)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.warmup = max(0, args.warmup)
         line = moe_reference(args) if args.workload == "moe" else dense_reference(args)
     else:
         args.warmup = max(3, args.warmup)
+        both = args.workload == "dense" and not args.no_moe and args.shape is None
+        if both:
+            import torch
+
+            shared_dist(torch).keep = True
         line = {"dense": dense_ours, "moe": moe_ours, "decode": decode_ours, "quantize": quantize_ours}[args.workload](
             args)
+        if both:
+            # BASELINE.json's metric has two halves: the GEMM (the line itself) and the MoE layer's tokens/s at
+            # 1/2/4/8 GPUs, which rides along as the line's "moe" object (same timing rules, fewer steps)
+            sub = argparse.Namespace(**vars(args))
+            sub.steps, sub.warmup, sub.no_cpu_baseline, sub.moe_config, sub.moe_tokens = min(args.steps, 20), 3, True, \
+                "dsv3", 0
+            moe_line = moe_ours(sub)
+            d = shared_dist(torch)
+            d.keep = False
+            d.close()
+            if line is not None and moe_line is not None:
+                line["moe"] = {k: moe_line[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup",
+                                                         "ms_per_step", "scaling", "config", "roofline", "e2e",
+                                                         "gpu_launches", "clocks", "device_status") if k in moe_line}
     if line is not None:
         print(json.dumps(line))
     return 0
