@@ -448,9 +448,9 @@ int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const f
         "fso_moe_combine_scatter: NULL pointer");
     FSO_REQUIRE((reinterpret_cast<uintptr_t>(dn) & 31u) == 0, "fso_moe_combine_scatter: dn must be 32-byte aligned");
     RowScatter const sc{recv_off, back_base, peer_back, static_cast<int>(world), coprime_multiplier(tokens)};
-    int64_t const threads = tokens * (h / 64);
-    FSO_REQUIRE(threads < (1ll << 31) - 4096, "fso_moe_combine_scatter: tokens * H/64 is beyond the kernel's index range");
-    combine_sparse_kernel<8><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, as_stream(stream)>>>(
+    // one CTA per row at a time, 128 threads over the row's 128-byte column groups; enough CTAs to fill the machine
+    int64_t const want = tokens < 148 * 32 ? tokens : 148 * 32;
+    combine_sparse_kernel<8><<<static_cast<unsigned>(want), 128, 0, as_stream(stream)>>>(
         static_cast<const uint8_t*>(dn), slot_of_flat, topk_w, tokens, static_cast<int>(topk), static_cast<int>(h * 2), sc);
     return launch_status("combine_sparse_kernel");
 }

@@ -381,90 +381,86 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const uint8_t* __rest
 }
 
 // The combine for rows most of whose top-k slots are -1 (one expert-parallel rank: a received row has only the ids
-// of the local experts). One thread owns 4 x 16 columns of one token and walks the live slots in ascending j, the
-// next live row's four 256-bit loads in flight while the current one is added: same sums, in the same order, as
-// combine_wide_kernel. Needs 32-byte aligned dn and H % 64 == 0; output rows go where `sc` says (scatter mode only).
+// of the local experts). One CTA walks rows (in the permuted order of RowScatter); per row the first warp reads the
+// top-k slots and weights once and compacts the live ones into shared memory (order kept), then every thread owns
+// 4 x 16 columns and adds the live rows in ascending j with the next row's loads in flight: the same sums, in the
+// same order, as combine_wide_kernel, with one index read per row instead of one per thread.
+// Needs 32-byte aligned dn and H % 64 == 0; output rows go where `sc` says (scatter mode only).
 template <int kMaxTopk>
-__global__ void __launch_bounds__(256) combine_sparse_kernel(const uint8_t* __restrict__ dn,
+__global__ void __launch_bounds__(128, 3) combine_sparse_kernel(const uint8_t* __restrict__ dn,
     const int32_t* __restrict__ slot_of_flat, const float* __restrict__ topk_w, int64_t tokens, int topk, int h_bytes,
     RowScatter sc)
 {
     constexpr int kGroups = 4;
     constexpr int kSpan = 32 * kGroups;
-    uint32_t const per_row = static_cast<uint32_t>(h_bytes) / kSpan;
-    uint32_t const idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= static_cast<uint32_t>(tokens) * per_row) return;
-    uint32_t const t32 = idx / per_row;
-    size_t const col = static_cast<size_t>(idx - t32 * per_row) * kSpan;
-    int64_t const t = static_cast<int64_t>(
-        (static_cast<unsigned long long>(t32) * sc.row_mul) % static_cast<unsigned long long>(tokens));
-    float acc[16 * kGroups];
-#pragma unroll
-    for (int i = 0; i < 16 * kGroups; ++i) acc[i] = 0.f;
-    // live (slot, weight) pairs, order kept
-    int slots[kMaxTopk];
-    float ws[kMaxTopk];
-    int live = 0;
-#pragma unroll
-    for (int j = 0; j < kMaxTopk; ++j) {
-        int const s = j < topk ? __ldg(slot_of_flat + t * topk + j) : -1;
-        float const w = j < topk ? __ldg(topk_w + t * topk + j) : 0.f;
-        if (s >= 0) {
-            // kMaxTopk is small: a select chain keeps the arrays in registers
-#pragma unroll
-            for (int q = 0; q < kMaxTopk; ++q)
-                if (q == live) {
-                    slots[q] = s;
-                    ws[q] = w;
-                }
-            ++live;
+    __shared__ int s_slot[2][kMaxTopk];
+    __shared__ float s_w[2][kMaxTopk];
+    __shared__ int s_live[2];
+    int const per_row = h_bytes / kSpan;
+    int buf = 0;
+    for (int64_t v = blockIdx.x; v < tokens; v += gridDim.x, buf ^= 1) {
+        int64_t const t = static_cast<int64_t>(
+            (static_cast<unsigned long long>(v) * sc.row_mul) % static_cast<unsigned long long>(tokens));
+        if (threadIdx.x < 32) {
+            int const j = threadIdx.x;
+            int const s = j < topk ? __ldg(slot_of_flat + t * topk + j) : -1;
+            float const w = j < topk ? __ldg(topk_w + t * topk + j) : 0.f;
+            unsigned const livemask = __ballot_sync(0xffffffffu, s >= 0);
+            if (s >= 0) {
+                int const pos = __popc(livemask & ((1u << j) - 1u));
+                s_slot[buf][pos] = s;
+                s_w[buf][pos] = w;
+            }
+            if (j == 0) s_live[buf] = __popc(livemask);
         }
-    }
-    auto load_row = [&](int q, uint32_t (&raw)[kGroups][8]) {
+        __syncthreads();          // double-buffered: the next row's header goes to the other buffer
+        int const live = s_live[buf];
         int s = 0;
+        while (s + 1 < sc.world && t >= __ldg(sc.recv_off + s + 1)) ++s;
+        uint8_t* const out_row = reinterpret_cast<uint8_t*>(__ldg(sc.peer_back + s))
+                                 + static_cast<size_t>(__ldg(sc.back_base + s) + (t - __ldg(sc.recv_off + s))) * h_bytes;
+        for (int c = threadIdx.x; c < per_row; c += blockDim.x) {
+            size_t const col = static_cast<size_t>(c) * kSpan;
+            float acc[16 * kGroups];
 #pragma unroll
-        for (int i = 0; i < kMaxTopk; ++i)
-            if (i == q) s = slots[i];
+            for (int i = 0; i < 16 * kGroups; ++i) acc[i] = 0.f;
+            uint32_t cur[kGroups][8], nxt[kGroups][8];
+            if (live > 0) {
 #pragma unroll
-        for (int g = 0; g < kGroups; ++g) ld_nc_256(dn + static_cast<size_t>(s) * h_bytes + col + 32 * g, raw[g]);
-    };
-    auto weight_of = [&](int q) {
-        float w = 0.f;
+                for (int g = 0; g < kGroups; ++g)
+                    ld_nc_256(dn + static_cast<size_t>(s_slot[buf][0]) * h_bytes + col + 32 * g, cur[g]);
+            }
+            for (int q = 0; q < live; ++q) {
+                if (q + 1 < live) {
 #pragma unroll
-        for (int i = 0; i < kMaxTopk; ++i)
-            if (i == q) w = ws[i];
-        return w;
-    };
-    uint32_t cur[kGroups][8], nxt[kGroups][8];
-    if (live > 0) load_row(0, cur);
-    for (int q = 0; q < live; ++q) {
-        if (q + 1 < live) load_row(q + 1, nxt);
-        float const w = weight_of(q);
+                    for (int g = 0; g < kGroups; ++g)
+                        ld_nc_256(dn + static_cast<size_t>(s_slot[buf][q + 1]) * h_bytes + col + 32 * g, nxt[g]);
+                }
+                float const w = s_w[buf][q];
 #pragma unroll
-        for (int g = 0; g < kGroups; ++g)
+                for (int g = 0; g < kGroups; ++g)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                acc[g * 16 + 2 * i] = fmaf(w, __uint_as_float(cur[g][i] << 16), acc[g * 16 + 2 * i]);
-                acc[g * 16 + 2 * i + 1] = fmaf(w, __uint_as_float(cur[g][i] & 0xFFFF0000u), acc[g * 16 + 2 * i + 1]);
+                    for (int i = 0; i < 8; ++i) {
+                        acc[g * 16 + 2 * i] = fmaf(w, __uint_as_float(cur[g][i] << 16), acc[g * 16 + 2 * i]);
+                        acc[g * 16 + 2 * i + 1]
+                            = fmaf(w, __uint_as_float(cur[g][i] & 0xFFFF0000u), acc[g * 16 + 2 * i + 1]);
+                    }
+#pragma unroll
+                for (int g = 0; g < kGroups; ++g)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) cur[g][i] = nxt[g][i];
             }
 #pragma unroll
-        for (int g = 0; g < kGroups; ++g)
+            for (int g = 0; g < kGroups; ++g) {
+                uint32_t o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) cur[g][i] = nxt[g][i];
-    }
-    int s = 0;
-    while (s + 1 < sc.world && t >= __ldg(sc.recv_off + s + 1)) ++s;
-    uint8_t* const out_row = reinterpret_cast<uint8_t*>(__ldg(sc.peer_back + s))
-                             + static_cast<size_t>(__ldg(sc.back_base + s) + (t - __ldg(sc.recv_off + s))) * h_bytes;
-#pragma unroll
-    for (int g = 0; g < kGroups; ++g) {
-        uint32_t o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = pack_bf16x2(acc[g * 16 + 2 * i], acc[g * 16 + 2 * i + 1]);
-        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"l"(out_row + col + 32 * g), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]),
-                     "r"(o[6]), "r"(o[7])
-                     : "memory");
+                for (int i = 0; i < 8; ++i) o[i] = pack_bf16x2(acc[g * 16 + 2 * i], acc[g * 16 + 2 * i + 1]);
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                             ::"l"(out_row + col + 32 * g), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]),
+                             "r"(o[5]), "r"(o[6]), "r"(o[7])
+                             : "memory");
+            }
+        }
     }
 }
 
