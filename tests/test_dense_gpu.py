@@ -239,9 +239,10 @@ def _outputs_in_child_process(shapes, env_extra, tag):
     import subprocess
     import sys
 
+    import tempfile
+
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    tmp = os.path.join(root, "gpurun_out")
-    os.makedirs(tmp, exist_ok=True)
+    tmp = tempfile.mkdtemp(prefix="fso_child_")
     base = os.path.join(tmp, tag)
     res = subprocess.run([sys.executable, "-c", _CHILD % (root, os.path.join(root, "tests"), tuple(shapes)), base],
                          env=dict(os.environ, **env_extra), capture_output=True, text=True, timeout=600)
@@ -335,9 +336,10 @@ def test_dependent_launch_chain_equals_plain_launches(fso, device_ok):
     import subprocess
     import sys
 
+    import tempfile
+
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    tmp = os.path.join(root, "gpurun_out")
-    os.makedirs(tmp, exist_ok=True)
+    tmp = tempfile.mkdtemp(prefix="fso_child_")
     got = {}
     for pdl in ("1", "0"):
         base = os.path.join(tmp, f"chain_pdl{pdl}")
