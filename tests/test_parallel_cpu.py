@@ -122,3 +122,34 @@ def test_shard_helpers():
     assert parallel.expert_shard(256, 8, 3) == (96, 128)
     with pytest.raises(ValueError):
         parallel.expert_shard(10, 4, 0)
+
+
+def test_transport_argument_is_checked_before_any_collective():
+    """An unknown transport, and the peer transport asked for together with what only the collective one takes,
+    are refused without touching the process group (none exists here)."""
+    from fish_scales_ops_b200 import parallel
+
+    h = torch.zeros(4, 128, dtype=torch.bfloat16)
+    ids = torch.zeros(4, 2, dtype=torch.int32)
+    w = torch.ones(4, 2)
+    with pytest.raises(ValueError):
+        parallel.expert_parallel_layer(h, None, ids, w, num_experts_global=8, transport="carrier pigeon")
+    with pytest.raises(ValueError):
+        parallel.expert_parallel_layer(h, None, ids, w, num_experts_global=8, transport="peer",
+                                       layer_fn=lambda *a: None)
+    with pytest.raises(ValueError):
+        parallel.expert_parallel_layer(h, None, ids, w, num_experts_global=8, transport="peer", micro_batches=2)
+
+
+def test_peer_buffer_layout_is_aligned_and_disjoint():
+    from fish_scales_ops_b200 import parallel
+
+    for world, cap, h, k in ((2, 1024, 512, 4), (8, 4096, 7168, 8), (4, 1024, 4096, 2)):
+        offs, total = parallel._PeerBuffers.layout(world, cap, h, k)
+        rows, back = world * cap, cap * min(k, world)
+        sizes = {"q": rows * h, "w": rows * (h // 128) * 4, "ids": rows * k * 4, "wt": rows * k * 4,
+                 "back": back * h * 2}
+        spans = sorted((offs[n], offs[n] + sizes[n]) for n in sizes)
+        assert all(o % 256 == 0 for o, _ in spans)
+        assert all(spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1))
+        assert spans[-1][1] <= total
