@@ -19,6 +19,7 @@ Workloads (``--workload``):
   decode    dense linears at M=16 over the four Llama-3-8B shapes, CUDA-graph replay over rotated weight copies
             (cold weights). Metric: achieved weight-stream GB/s (worst of the four shapes).
   quantize  the activation quantizer alone on [8192, 4096]. Metric: GB/s.
+  requant   the block-FP8 -> MXFP8 requantization kernel of prepare_weight alone on [24576, 7168]. Metric: GB/s.
 
 ``--impl reference`` times the reference's CPU statement of the same workload (the fp32 dequantize-then-matmul
 oracle under ``oracle/``, the only thing that runs there) on this box's host cores, on a bounded sample, and prints
@@ -602,13 +603,49 @@ def quantize_ours(args):
     return line
 
 
+def requant_ours(args):
+    """Block-FP8 checkpoint -> MXFP8 at load (BASELINE.json configs[2], the largest shape N = 24576, K = 7168):
+    the requantization kernel alone under CUDA-graph replay over rotated checkpoints. Algorithmic bytes per element:
+    1 read + (1 + 1/32) written, + 4 per 128 x 128 tile."""
+    import torch
+
+    import fish_scales_ops_b200 as fso
+    from fish_scales_ops_b200 import _ops
+
+    d = shared_dist(torch)
+    fso.build()
+    n, k = 24576, 7168
+    copies = 2
+    g = torch.Generator(device="cuda").manual_seed(5)
+    ws = [torch.randn(n, k, generator=g, device="cuda", dtype=torch.bfloat16).clamp_(-448, 448).to(torch.float8_e4m3fn)
+          for _ in range(copies)]
+    sc = torch.exp2(-8.0 + 4.0 * torch.rand(n // 128, k // 128, generator=g, device="cuda"))
+    with ClockSampler(d.local) as sampler:
+        us = graph_replay_us(torch, lambda i: _ops.requant_block_fp8(ws[i % copies], sc), copies, max(5, args.steps // 4))
+    clocks = sampler.summary()
+    nbytes = n * k * (2 + 1 / 32) + 4 * (n // 128) * (k // 128)
+    pk = peaks()
+    line = base_line(args, d, "requant_bs128_to_mxfp8_gbs", "GB/s", nbytes / us / 1e3, us / 1e3, "strong",
+                     "fp8_e4m3 x f32 -> fp8_e4m3",
+                     {"workload": f"block-FP8 (128x128 fp32 scales) -> MXFP8 requantization of [{n}, {k}], {copies} "
+                                  f"rotated checkpoints", "l2": "2 x 176 MB inputs + outputs exceed L2"})
+    line["roofline"] = {"bound": "hbm", "kernel": "requant_bs128_kernel", "achieved": nbytes / us / 1e3,
+                        "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": nbytes / us / 1e3 / pk["hbm_gbs"],
+                        "traffic": None, "peak_source": f"{pk['source']} copy bandwidth"}
+    line["gpu_launches"] = copies * args.steps
+    line["clocks"] = clocks
+    line["device_status"] = _ops.device_status()
+    d.close()
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize", "requant"])
     ap.add_argument("--moe-config", default="dsv3", choices=sorted(MOE_CONFIGS))
     ap.add_argument("--moe-tokens", type=int, default=0, help="moe workload: tokens per GPU override")
     ap.add_argument("--decode-m", type=int, default=16)
@@ -627,8 +664,8 @@ def main():
             import torch
 
             shared_dist(torch).keep = True
-        line = {"dense": dense_ours, "moe": moe_ours, "decode": decode_ours, "quantize": quantize_ours}[args.workload](
-            args)
+        line = {"dense": dense_ours, "moe": moe_ours, "decode": decode_ours, "quantize": quantize_ours,
+                "requant": requant_ours}[args.workload](args)
         if both:
             # BASELINE.json's metric has two halves: the GEMM (the line itself) and the MoE layer's tokens/s at
             # 1/2/4/8 GPUs, which rides along as the line's "moe" object (same timing rules, fewer steps)

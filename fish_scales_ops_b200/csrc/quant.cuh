@@ -422,10 +422,80 @@ __global__ void __launch_bounds__(256) requant_bs128_kernel(const uint4* __restr
     }
 }
 
+// The same with 32 codes per thread (one 256-bit load, one 256-bit store): one lane per 1x32 block, so the amax
+// needs no shuffle, 4 lanes per scale word, 32-bit index arithmetic. Needs 32-byte aligned wq / q and
+// n * K/128 * 4 < 2^31.
+__global__ void __launch_bounds__(256) requant_bs128_wide_kernel(const uint8_t* __restrict__ wq,
+    const float* __restrict__ s128, uint8_t* __restrict__ q, uint32_t* __restrict__ sf, uint32_t n, uint32_t kb,
+    uint32_t interleave_i)
+{
+    uint32_t const sub = threadIdx.x & 3;
+    uint32_t const c = (blockIdx.x * blockDim.x + threadIdx.x) >> 2;        // chunk (row, kp)
+    bool const live = c < n * kb;
+    uint32_t const row = live ? c / kb : 0;
+    uint32_t const kp = live ? c - row * kb : 0;
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = 0;
+    float s = 0.f;
+    if (live) {
+        uint32_t src = row;
+        if (interleave_i > 0) {
+            uint32_t const two_i = 2 * interleave_i;
+            uint32_t const g = src / two_i, o = src - g * two_i;
+            src = g * two_i + ((o & 1) ? interleave_i + (o >> 1) : (o >> 1));
+        }
+        ld_nc_256(wq + (static_cast<size_t>(src) * kb + kp) * 128 + sub * 32, w);
+        s = __ldg(s128 + static_cast<size_t>(src >> 7) * kb + kp);
+    }
+    float f[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            __half2_raw const hr = __nv_cvt_fp8x2_to_halfraw2(
+                static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
+            float2 const p = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+            float const a = __bfloat162float(__float2bfloat16_rn(__fmul_rn(p.x, s)));
+            float const b = __bfloat162float(__float2bfloat16_rn(__fmul_rn(p.y, s)));
+            f[i * 4 + h * 2] = a;
+            f[i * 4 + h * 2 + 1] = b;
+            amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+        }
+    }
+    amax = fmaxf(amax, 1e-10f);
+    float qs;
+    uint32_t const byte = e8m0_from_amax(amax, qs);
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        o[i] = fp8x4(__fmul_rn(f[4 * i], qs), __fmul_rn(f[4 * i + 1], qs), __fmul_rn(f[4 * i + 2], qs),
+            __fmul_rn(f[4 * i + 3], qs));
+    uint32_t word = byte << (8 * sub);
+    word |= __shfl_xor_sync(0xFFFFFFFFu, word, 1);
+    word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
+    if (live) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"l"(q + (static_cast<size_t>(row) * kb + kp) * 128 + sub * 32), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                     "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                     : "memory");
+        if (sub == 0) sf[sf_word_index(row, kp, kb)] = word;
+    }
+}
+
 inline int launch_requant_bs128(const void* wq, const float* s128, void* q, void* sf, int64_t n, int64_t k,
     int64_t interleave_i, cudaStream_t stream)
 {
     int const kb = static_cast<int>(k / 128);
+    if (((reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(q)) & 31u) == 0
+        && n * kb * 4 < (1ll << 31) - 4096 && interleave_i < (1ll << 30)) {
+        int64_t const wblocks = (n * kb * 4 + 255) / 256;
+        requant_bs128_wide_kernel<<<static_cast<unsigned>(wblocks), 256, 0, stream>>>(static_cast<const uint8_t*>(wq),
+            s128, static_cast<uint8_t*>(q), static_cast<uint32_t*>(sf), static_cast<uint32_t>(n),
+            static_cast<uint32_t>(kb), static_cast<uint32_t>(interleave_i));
+        return launch_status("fso_requant_bs128_to_mx");
+    }
     int64_t const blocks = (n * kb * 8 + 255) / 256;
     requant_bs128_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(wq), s128,
         static_cast<uint4*>(q), static_cast<uint32_t*>(sf), n, kb, interleave_i);

@@ -112,3 +112,21 @@ def test_quantizer_narrow_and_wide_kernels_agree(fso, oracle, device_ok):
     for t in (narrow, wide):
         q, s = _ops.quantize_1x32_fp8(t)
         assert np.array_equal(inputs.to_np_u8(q), oq) and np.array_equal(inputs.to_np_u32(s), os_)
+
+
+def test_requant_narrow_and_wide_kernels_agree(fso, oracle, device_ok):
+    """A checkpoint on a 32-byte boundary takes the 256-bit kernel, one 16 bytes past it the 128-bit kernel: same
+    bytes, and both equal the oracle."""
+    from fish_scales_ops_b200 import _ops
+
+    n, k = 384, 512
+    wq, s = inputs.block_fp8_checkpoint(n, k, 21)
+    raw = torch.empty(n * k + 16, dtype=torch.uint8, device="cuda")
+    shifted = raw[16:].view(torch.float8_e4m3fn).view(n, k)
+    shifted.copy_(wq.cuda())
+    assert shifted.data_ptr() % 32 == 16
+    q_wide, sf_wide = _ops.requant_block_fp8(wq.cuda(), s.cuda())
+    q_narrow, sf_narrow = _ops.requant_block_fp8(shifted, s.cuda())
+    assert torch.equal(q_wide.view(torch.uint8), q_narrow.view(torch.uint8)) and torch.equal(sf_wide, sf_narrow)
+    oq, osf = oracle.requant_bs128(wq, s)
+    assert np.array_equal(inputs.to_np_u8(q_wide), oq) and np.array_equal(inputs.to_np_u32(sf_wide), osf)
