@@ -166,3 +166,20 @@ def test_router_oracle_matches_torch_softmax_topk(oracle):
         ids_p, _, _ = oracle.router_topk(lg[:, :e], k, True)
         assert np.array_equal(ids_m[:m // 2], emap[ids_p[:m // 2]])
         assert (ids_m[m // 2:] == emap[e]).all() and (w_m[m // 2:] == 0).all()
+
+
+def test_dense_epilogue_oracle_known_answers(oracle):
+    """The epilogue oracle on values whose results are known: a zero bias of either sign changes nothing (not even
+    the sign of a zero accumulator), erf-GELU equals torch's, and the order is act(acc + bias) + residual."""
+    acc = torch.tensor([[0.0, -0.0, 1.5, -2.0], [3.0, -0.25, 0.0, 8.0]], dtype=torch.float32)
+    for zero in (0.0, -0.0):
+        out = oracle.dense_epilogue(acc, torch.full((4,), zero, dtype=torch.bfloat16))
+        assert torch.equal(out.view(torch.int32), acc.view(torch.int32))
+    bias = torch.tensor([0.5, -1.0, 0.0, 2.0], dtype=torch.bfloat16)
+    res = torch.tensor([[1.0, 1.0, 1.0, 1.0], [-2.0, 0.5, 0.25, 0.0]], dtype=torch.bfloat16)
+    out = oracle.dense_epilogue(acc, bias, res, "gelu_erf")
+    want = torch.nn.functional.gelu(acc + bias.float()) + res.float()
+    assert float((out - want).abs().max()) <= 1e-6
+    assert torch.equal(oracle.dense_epilogue(acc, None, res, None), acc + res.float())
+    with pytest.raises(ValueError):
+        oracle.dense_epilogue(acc, None, None, "gelu_tanh")
