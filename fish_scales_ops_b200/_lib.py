@@ -18,6 +18,7 @@ SIGNATURES = {
     "fso_b200_version": [],
     "fso_b200_last_error": [],
     "fso_b200_device_status": [ctypes.POINTER(ctypes.c_int)],
+    "fso_b200_selftest_wait_expires": [_c_i64, _c_p],
     "fso_quantize_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
     "fso_requant_bs128_to_mx": [_c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
     "fso_pack_ue8m0": [_c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p],

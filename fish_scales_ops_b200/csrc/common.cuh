@@ -22,6 +22,7 @@ constexpr int FSO_DEV_WAIT_PRODUCER = 0x100;   // TMA producer waited for a free
 constexpr int FSO_DEV_WAIT_MMA_FULL = 0x200;   // MMA issuer waited for a filled stage
 constexpr int FSO_DEV_WAIT_MMA_TMEM = 0x300;   // MMA issuer waited for a drained accumulator
 constexpr int FSO_DEV_WAIT_EPILOGUE = 0x400;   // epilogue waited for a finished accumulator
+constexpr int FSO_DEV_SELFTEST_WAIT = 0x700;   // the self-test's wait on a barrier nothing arrives at ran out
 
 int sm_count();                                 // SMs of the current device (cached per device)
 int current_device();
@@ -39,15 +40,18 @@ int current_device();
         cudaError_t e__ = (expr);                                                                                   \
         if (e__ != cudaSuccess) {                                                                                   \
             ::fso::set_error("%s failed: %s", #expr, cudaGetErrorString(e__));                                      \
+            (void)cudaGetLastError(); /* the failure is reported here: later calls must not see it again */        \
             return static_cast<int>(e__);                                                                           \
         }                                                                                                           \
     } while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Result of the launches just made. cudaGetLastError() also clears the error, so that a failed launch is reported by
+// the call that caused it and by no later one.
 inline int launch_status(const char* what)
 {
-    cudaError_t e = cudaPeekAtLastError();
+    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("%s: launch failed: %s", what, cudaGetErrorString(e));
         return static_cast<int>(e);

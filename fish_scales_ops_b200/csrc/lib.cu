@@ -66,6 +66,29 @@ int fso_b200_device_status(int* status)
     return 0;
 }
 
+// Self-test of the bounded waits: one thread waits on an mbarrier that nothing ever arrives at, for at most
+// `limit_cycles` SM cycles, then records FSO_DEV_SELFTEST_WAIT in the device status word and returns, exactly as a
+// wait of the GEMM kernels does when it runs out. Nothing can hang: the wait ends by itself.
+__global__ void selftest_wait_kernel(long long limit_cycles)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    uint32_t const b = smem_u32(&bar);
+    mbar_init(b, 1);
+    mbar_fence_init();
+    long long const t0 = clock64();
+    bool done = false;
+    while (!done && clock64() - t0 <= limit_cycles) done = mbar_try_wait(b, 0);
+    if (!done) atomicCAS(&g_dev_status, 0, FSO_DEV_SELFTEST_WAIT);
+}
+
+int fso_b200_selftest_wait_expires(int64_t limit_cycles, void* stream)
+{
+    FSO_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll,
+        "fso_b200_selftest_wait_expires: limit_cycles must be in (0, 2e9] (about a second of SM clock at most)");
+    selftest_wait_kernel<<<1, 1, 0, as_stream(stream)>>>(static_cast<long long>(limit_cycles));
+    return launch_status("selftest_wait_kernel");
+}
+
 int fso_quantize_1x32(const void* x, void* xq, void* sf, int64_t m, int64_t k, int64_t interleave_i, void* stream)
 {
     FSO_REQUIRE(m >= 0 && k > 0 && k % 128 == 0, "fso_quantize_1x32: K = %lld must be a positive multiple of 128",
@@ -209,38 +232,56 @@ int fso_moe_plan_make(int64_t tokens, int64_t topk, int64_t num_experts, fso_moe
     return 0;
 }
 
-int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_experts, int64_t num_blocks,
-    int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* scratch,
-    int64_t scratch_bytes, void* stream)
+// Shared memory of the routing kernels: 64 * E bytes of dynamic shared memory ([32 warps][E] uint16) on top of up to
+// 8.3 KB of static arrays, which passes the 48 KB a kernel gets without opting in from E = 638 on. The opt-in is made
+// once per device for the largest E the entry points accept, by the first routing call on that device whatever its
+// size (so a small warm-up call prepares every later one; make it outside stream capture).
+static int route_prepare_device()
 {
-    fso_moe_plan pl;
-    int const rc = fso_moe_plan_make(tokens, topk, num_experts, &pl);
-    if (rc != 0) return rc;
-    FSO_REQUIRE(num_blocks >= pl.num_blocks, "fso_moe_route: num_blocks = %lld is below the bound %lld of this call",
-        static_cast<long long>(num_blocks), static_cast<long long>(pl.num_blocks));
-    FSO_REQUIRE(masked_m && blk0 && blk_expert && (pl.pairs == 0 || (ids && slot_of_flat)), "fso_moe_route: NULL pointer");
-    cudaStream_t const st = as_stream(stream);
-    int const e = static_cast<int>(num_experts), nb = static_cast<int>(num_blocks), pairs = static_cast<int>(pl.pairs);
+    static std::atomic<uint64_t> done{0};
+    int const dev = current_device();
+    uint64_t const bit = 1ull << (dev & 63);
+    if ((done.load(std::memory_order_acquire) & bit) == 0) {
+        int const smem = 64 * 1024;
+        FSO_CUDA(cudaFuncSetAttribute(route_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        FSO_CUDA(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        FSO_CUDA(cudaFuncSetAttribute(route_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        done.fetch_or(bit, std::memory_order_release);
+    }
+    return 0;
+}
+
+static int launch_route(const int32_t* ids, int pairs, int e, int nb, int32_t* masked_m, int32_t* blk0,
+    int32_t* slot_of_flat, int32_t* blk_expert, int32_t* seg, cudaStream_t st, const char* what)
+{
     size_t const smem = static_cast<size_t>(64) * e;   // [32][E] uint16
     if (pairs <= kRouteSeg) {
         route_small_kernel<<<1, kRouteSeg, smem, st>>>(ids, pairs, e, nb, masked_m, blk0, slot_of_flat, blk_expert);
         return launch_status("route_small_kernel");
     }
-    FSO_REQUIRE(scratch != nullptr && scratch_bytes >= pl.route_scratch_bytes && (reinterpret_cast<uintptr_t>(scratch) & 3u) == 0,
-        "fso_moe_route: this call needs %lld bytes of 4-byte aligned scratch", static_cast<long long>(pl.route_scratch_bytes));
     int const segs = (pairs + kRouteSeg - 1) / kRouteSeg;
-    int32_t* seg = static_cast<int32_t*>(scratch);
-    static std::atomic<uint64_t> done_count{0}, done_place{0};
-    if (smem > 48 * 1024) {
-        int r2 = ensure_smem_attr(route_count_kernel, static_cast<int>(smem), done_count);
-        if (r2 != 0) return r2;
-        r2 = ensure_smem_attr(route_place_kernel, static_cast<int>(smem), done_place);
-        if (r2 != 0) return r2;
-    }
     route_count_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg);
     route_scan_kernel<<<1, kRouteSeg, 0, st>>>(seg, segs, e, nb, masked_m, blk0, blk_expert);
     route_place_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg, blk0, slot_of_flat);
-    return launch_status("route kernels");
+    return launch_status(what);
+}
+
+int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_experts, int64_t num_blocks,
+    int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* scratch,
+    int64_t scratch_bytes, void* stream)
+{
+    fso_moe_plan pl;
+    int rc = fso_moe_plan_make(tokens, topk, num_experts, &pl);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(num_blocks >= pl.num_blocks, "fso_moe_route: num_blocks = %lld is below the bound %lld of this call",
+        static_cast<long long>(num_blocks), static_cast<long long>(pl.num_blocks));
+    FSO_REQUIRE(masked_m && blk0 && blk_expert && (pl.pairs == 0 || (ids && slot_of_flat)), "fso_moe_route: NULL pointer");
+    FSO_REQUIRE(pl.pairs <= kRouteSeg
+            || (scratch != nullptr && scratch_bytes >= pl.route_scratch_bytes && (reinterpret_cast<uintptr_t>(scratch) & 3u) == 0),
+        "fso_moe_route: this call needs %lld bytes of 4-byte aligned scratch", static_cast<long long>(pl.route_scratch_bytes));
+    if ((rc = route_prepare_device()) != 0) return rc;
+    return launch_route(ids, static_cast<int>(pl.pairs), static_cast<int>(num_experts), static_cast<int>(num_blocks),
+        masked_m, blk0, slot_of_flat, blk_expert, static_cast<int32_t*>(scratch), as_stream(stream), "route kernels");
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -255,7 +296,8 @@ int fso_moe_route(const int32_t* ids, int64_t tokens, int64_t topk, int64_t num_
 //
 // The array's name is only a host-side stand-in in host code, not a device address, so the device address is looked
 // up once per device with cudaGetSymbolAddress (with that device current) and handed to the kernels. That lookup
-// happens in the first call made on a device; make that first call outside any stream capture.
+// happens in the first call made on a device, whatever that call's size; make that first call outside any stream
+// capture.
 // Limits: tokens * topk <= kRouteStaticMaxPairs; larger calls are refused. The array is shared by every call and
 // keeps the previous call's contents; the kernels overwrite every word they later read, so nothing needs clearing,
 // but two calls that overlap on the GPU (different streams) race on it: serialize them.
@@ -284,7 +326,7 @@ int fso_moe_route_noalloc(const int32_t* ids, int64_t tokens, int64_t topk, int6
     int32_t* masked_m, int32_t* blk0, int32_t* slot_of_flat, int32_t* blk_expert, void* stream)
 {
     fso_moe_plan pl;
-    int const rc = fso_moe_plan_make(tokens, topk, num_experts, &pl);
+    int rc = fso_moe_plan_make(tokens, topk, num_experts, &pl);
     if (rc != 0) return rc;
     FSO_REQUIRE(pl.pairs <= kRouteStaticMaxPairs,
         "fso_moe_route_noalloc: tokens * topk = %lld exceeds the %lld pairs its built-in scratch covers; use "
@@ -293,28 +335,13 @@ int fso_moe_route_noalloc(const int32_t* ids, int64_t tokens, int64_t topk, int6
         static_cast<long long>(num_blocks), static_cast<long long>(pl.num_blocks));
     FSO_REQUIRE(masked_m && blk0 && blk_expert && (pl.pairs == 0 || (ids && slot_of_flat)),
         "fso_moe_route_noalloc: NULL pointer");
-    cudaStream_t const st = as_stream(stream);
-    int const e = static_cast<int>(num_experts), nb = static_cast<int>(num_blocks), pairs = static_cast<int>(pl.pairs);
-    size_t const smem = static_cast<size_t>(64) * e;
-    if (pairs <= kRouteSeg) {
-        route_small_kernel<<<1, kRouteSeg, smem, st>>>(ids, pairs, e, nb, masked_m, blk0, slot_of_flat, blk_expert);
-        return launch_status("route_small_kernel");
-    }
+    // per-device set-up first, whatever the size of this call: the address of the built-in array and the routing
+    // kernels' shared-memory opt-in, so that any first call on a device warms it for every later one
     int32_t* seg = nullptr;
-    int const rp = route_static_scratch_ptr(&seg);
-    if (rp != 0) return rp;
-    int const segs = (pairs + kRouteSeg - 1) / kRouteSeg;
-    static std::atomic<uint64_t> done_count{0}, done_place{0};
-    if (smem > 48 * 1024) {
-        int r2 = ensure_smem_attr(route_count_kernel, static_cast<int>(smem), done_count);
-        if (r2 != 0) return r2;
-        r2 = ensure_smem_attr(route_place_kernel, static_cast<int>(smem), done_place);
-        if (r2 != 0) return r2;
-    }
-    route_count_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg);
-    route_scan_kernel<<<1, kRouteSeg, 0, st>>>(seg, segs, e, nb, masked_m, blk0, blk_expert);
-    route_place_kernel<<<segs, kRouteSeg, smem, st>>>(ids, pairs, e, seg, blk0, slot_of_flat);
-    return launch_status("route kernels (built-in scratch)");
+    if ((rc = route_static_scratch_ptr(&seg)) != 0) return rc;
+    if ((rc = route_prepare_device()) != 0) return rc;
+    return launch_route(ids, static_cast<int>(pl.pairs), static_cast<int>(num_experts), static_cast<int>(num_blocks),
+        masked_m, blk0, slot_of_flat, blk_expert, seg, as_stream(stream), "route kernels (built-in scratch)");
 }
 
 int fso_moe_gather_quant(const void* hidden, const int32_t* slot_of_flat, int64_t tokens, int64_t topk, int64_t h,
@@ -449,7 +476,8 @@ int fso_moe_combine_scatter(const void* dn, const int32_t* slot_of_flat, const f
     FSO_REQUIRE((reinterpret_cast<uintptr_t>(dn) & 31u) == 0, "fso_moe_combine_scatter: dn must be 32-byte aligned");
     RowScatter const sc{recv_off, back_base, peer_back, static_cast<int>(world), coprime_multiplier(tokens)};
     // one CTA per row at a time, 128 threads over the row's 128-byte column groups; enough CTAs to fill the machine
-    int64_t const want = tokens < 148 * 32 ? tokens : 148 * 32;
+    int64_t const cap = static_cast<int64_t>(sm_count()) * 32;
+    int64_t const want = tokens < cap ? tokens : cap;
     combine_sparse_kernel<8><<<static_cast<unsigned>(want), 128, 0, as_stream(stream)>>>(
         static_cast<const uint8_t*>(dn), slot_of_flat, topk_w, tokens, static_cast<int>(topk), static_cast<int>(h * 2), sc);
     return launch_status("combine_sparse_kernel");

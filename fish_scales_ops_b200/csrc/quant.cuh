@@ -19,7 +19,8 @@ namespace fso {
 // Scale byte and quant scale of a block from its amax (already floored at 1e-10f). Division-free form of
 // b = exp(1 / (448 / amax)) + (mantissa != 0): with E, f the exponent and mantissa fields of amax,
 // b = E - (f <= 0x600000 ? 8 : 7), clamped to [0, 254]; quant scale 2^(127 - b). Equal to the two-division form
-// for every fp32 amax >= 1e-10f (checked exhaustively on the host).
+// for every finite fp32 amax >= 1e-10f (checked exhaustively on the host). An infinite amax (a block that holds an
+// Inf) gives 254 like the division form does: 448 / Inf = 0, 1 / 0 = Inf, exponent field 255, capped.
 __device__ __forceinline__ uint32_t e8m0_from_amax(float amax, float& quant_scale)
 {
     uint32_t const bits = __float_as_uint(amax);
@@ -27,6 +28,7 @@ __device__ __forceinline__ uint32_t e8m0_from_amax(float amax, float& quant_scal
     uint32_t const f = bits & 0x7FFFFFu;
     int byte = e - (f <= 0x600000u ? 8 : 7);
     byte = max(0, min(254, byte));
+    if (e == 255) byte = 254;
     uint32_t qbits = static_cast<uint32_t>(254 - byte) << 23;
     if (byte == 254) qbits = 0x00400000u;    // 2^-127, a subnormal
     if (byte == 0) qbits = 0x3F800000u;
@@ -59,14 +61,39 @@ __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b)
     return __vmaxu2(a & 0x7FFF7FFFu, b & 0x7FFF7FFFu);
 }
 
+// |.| patterns of the two halves with NaN halves replaced by zero. The block amax is a chain of fmaxf in the
+// reference (csrc/gemm/ops/quant_kernels.cu:625-633), which passes over NaNs: a NaN never becomes the amax. On bit
+// patterns a NaN (> 0x7F80) would win the integer max, so a block whose pattern max says "NaN present" is reduced
+// again through this form (rare path).
+__device__ __forceinline__ uint32_t abs_bf16x2_drop_nan(uint32_t a)
+{
+    uint32_t const m = a & 0x7FFF7FFFu;
+    return m & ~__vcmpgtu2(m, 0x7F807F80u);
+}
+
+// max over the halves of n words
+template <int N>
+__device__ __forceinline__ uint32_t absmax_words(uint32_t const (&w)[N], bool drop_nan)
+{
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) m = __vmaxu2(m, drop_nan ? abs_bf16x2_drop_nan(w[i]) : (w[i] & 0x7FFF7FFFu));
+    return max(m & 0xFFFFu, m >> 16);
+}
+
 // Quantizes the 8 bf16 values of `v` (one 16-byte load) of a 32-element block shared by 4 adjacent lanes.
 // Returns the 8 codes in `out` and the block's byte (same value on the 4 lanes).
 __device__ __forceinline__ uint32_t quant8_shared4(uint4 const& v, uint2& out)
 {
-    uint32_t m = absmax_bf16x2(absmax_bf16x2(v.x, v.y), absmax_bf16x2(v.z, v.w));
-    m = max(m & 0xFFFFu, m >> 16);
+    uint32_t const w4[4] = {v.x, v.y, v.z, v.w};
+    uint32_t m = absmax_words(w4, false);
     m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    if (__any_sync(0xFFFFFFFFu, m > 0x7F80u)) {            // a NaN somewhere in the warp's blocks: leave NaNs out
+        m = absmax_words(w4, true);
+        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    }
     float const amax = fmaxf(__uint_as_float(m << 16), 1e-10f);
     float qs;
     uint32_t const byte = e8m0_from_amax(amax, qs);
@@ -155,10 +182,12 @@ __device__ __forceinline__ void ld_nc_256(const void* p, uint32_t (&r)[8])
 
 __device__ __forceinline__ uint32_t quant16_shared2(uint32_t const (&v)[8], uint4& out)
 {
-    uint32_t m = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(v[0], v[1]), absmax_bf16x2(v[2], v[3])),
-        absmax_bf16x2(absmax_bf16x2(v[4], v[5]), absmax_bf16x2(v[6], v[7])));
-    m = max(m & 0xFFFFu, m >> 16);
+    uint32_t m = absmax_words(v, false);
     m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    if (__any_sync(0xFFFFFFFFu, m > 0x7F80u)) {            // a NaN somewhere in the warp's blocks: leave NaNs out
+        m = absmax_words(v, true);
+        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    }
     float const amax = fmaxf(__uint_as_float(m << 16), 1e-10f);
     float qs;
     uint32_t const byte = e8m0_from_amax(amax, qs);

@@ -214,7 +214,9 @@ def _empty_act_scale(m, k: int, device) -> torch.Tensor:
 
 
 def include_dir() -> str:
-    """The directory that holds ``fso_b200.h`` (the C ABI, whose header comment states the activation layout)."""
+    """The directory that holds ``fso_b200_activation_contract.h`` (the activation contract as compilable C / C++ /
+    CUDA: scale-byte rule, E4M3 conversion, word packing and the index formula, for producers of pre-quantized
+    activations) and ``fso_b200.h`` (the C ABI)."""
     return os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "include")
 
 
@@ -239,7 +241,7 @@ def activation_contract() -> dict:
         "rule": "per 32-element block of a row: amax = max |x| in fp32, floored at 1e-10f; q = 448.f / amax; "
                 "d = 1.f / q; b = exp_field(d) + (mantissa(d) != 0), capped at 254; code = "
                 "cvt.rn.satfinite.e4m3(x * 2^(127 - b)); word(m, kp) = b0 | b1 << 8 | b2 << 16 | b3 << 24",
-        "header": "fso_b200.h",
+        "header": "fso_b200_activation_contract.h",
         "include_dir": include_dir(),
     }
 
@@ -533,9 +535,10 @@ def linear(x, weight, *, bias=None, x_scale=None, residual=None, activation=None
     """``y = x @ W^T`` for a prepared weight: bf16 ``[..., N]`` (python/fish_scales_ops/dense/__init__.py:1153-1209).
 
     ``x`` is bf16 ``[..., K]`` (quantized inside the op) or, with ``x_scale``, the float8_e4m3fn ``[M, K]`` of
-    :func:`quantize_activation`. ``bias`` / ``residual`` / ``activation`` are validated; a call that sets one is
-    refused with NotImplementedError before anything is launched. Nothing in the call synchronizes the device, and
-    it can be captured into a CUDA graph after one eager call of the same shape."""
+    :func:`quantize_activation`. ``bias`` (bf16 ``[N]``), ``activation`` (``"gelu_erf"``) and ``residual`` (bf16, the
+    result's shape) are applied in the GEMM's epilogue to the fp32 accumulator, in that order, before the one
+    rounding to bf16. Nothing in the call synchronizes the device, and it can be captured into a CUDA graph after
+    one eager call of the same shape."""
     where = arch_label(device_arch())
     _check_handle(weight, where, "fso.dense.linear")
     x2, lead = _flatten_x(x, weight, x_scale, where, "fso.dense.linear")

@@ -11,7 +11,10 @@ cover the two ways the path shards:
   with the ids of other ranks' experts rewritten to -1 (the layer skips them at no cost and returns a partial sum),
   the partial rows travel back (all-to-all-v combine) and the source rank adds them in rank order in fp32.
 
-Kernels only ever read this GPU's memory: rows arrive through NCCL before any kernel touches them.
+Kernels only ever READ this GPU's memory. With the default transport the rows are stored into the destination GPU's
+receive buffers by this library's own kernels (plain peer stores, ordered by two stream-ordered collectives); with
+``transport="collective"`` they travel through NCCL all-to-all-v. Either way a kernel touches a row only once it
+lies in its own GPU's memory.
 """
 import dataclasses
 import os
@@ -173,7 +176,9 @@ def _peer_buffers(group, world: int, tokens_max: int, h: int, k: int, device) ->
     """The buffers for this (group, H, k), grown (by at least 2x) when a batch needs more rows than they hold.
     ``tokens_max`` is the largest token count over the ranks, which every rank knows, so that every rank takes the
     same decision and the collective allocation matches."""
-    key = (id(group) if group is not None else 0, h, k, str(device))
+    # keyed on the group's member ranks, not on id(group): Python may hand a destroyed group's id to a new one
+    members = tuple(dist.get_process_group_ranks(group)) if group is not None else ("world", world)
+    key = (members, h, k, str(device))
     have = _PEER_BUFFERS.get(key)
     if have is not None and have.cap_tokens >= tokens_max:
         return have

@@ -35,6 +35,13 @@ const char* fso_b200_last_error(void);
  * out inside a kernel. Synchronizes the device; meant for tests and health checks, never for the hot path. */
 int fso_b200_device_status(int* status);
 
+/* Health check of the bounded device-side waits: launches one thread that waits, for at most limit_cycles SM cycles
+ * (0 < limit_cycles <= 2e9), on an mbarrier nothing arrives at; when the wait has run out the thread records the
+ * status 0x700 (read it with fso_b200_device_status) and the kernel returns. The device context stays usable.
+ * No counterpart in the reference, whose device waits are unbounded (e.g. the work-stealing scheduler's spin,
+ * csrc/gemm/include/blockscale_gemm/arch/sm100/mxfp8/slot_work_stealing.cuh). */
+int fso_b200_selftest_wait_expires(int64_t limit_cycles, void* stream);
+
 /* bf16 [M, K] -> e4m3 [M, K] + scale words (1x32 MXFP8 rule, bit-exact with the reference).
  * interleave_i > 0: x is G stacked [2*I, K] expert matrices in [gate; up] row order and output rows 2j / 2j+1 of
  * each expert take its rows j / I+j (the fused-FC1 weight order).

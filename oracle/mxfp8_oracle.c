@@ -111,6 +111,7 @@ uint8_t orc_e8m0_from_amax_int(float amax, float* quant_scale)
     int byte = e - (f <= 0x600000u ? 8 : 7);
     if (byte < 0) byte = 0;
     if (byte > 254) byte = 254;
+    if (e == 255) byte = 254;      /* amax = Inf: the divide form gives 448 / Inf = 0, 1 / 0 = Inf, field 255, capped */
     *quant_scale = byte == 254 ? u2f(0x00400000u) : u2f((uint32_t)(254 - byte) << 23);
     if (byte == 0) *quant_scale = 1.f;
     return (uint8_t)byte;

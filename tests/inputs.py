@@ -21,7 +21,9 @@ def weight(n: int, k: int, seed: int) -> torch.Tensor:
 def edge_activation() -> torch.Tensor:
     """bf16 [130, 256] covering the quantizer's corner cases: all-zero blocks, values under the amax floor, the
     largest finite bf16, exact powers of two and the 1.75 * 2^e boundary of the scale-byte rule, negative zero,
-    and a ragged row count (130 is not a multiple of 128, so the padded rows' words are exercised)."""
+    non-finite values (a NaN never becomes a block's amax, the reference's fmaxf chain passes over it; an Inf makes
+    the amax infinite and the scale byte 254), and a ragged row count (130 is not a multiple of 128, so the padded
+    rows' words are exercised)."""
     x = torch.randn(130, 256, generator=gen(1234), dtype=torch.float32)
     x[0] = 0.0
     x[1, :32] = 1e-12
@@ -40,6 +42,17 @@ def edge_activation() -> torch.Tensor:
     x[7, ::2] = 0.0
     x[8, 128:] = 1e-10
     x[9, :] = 9.9e-11
+    x[10, 3] = float("nan")                     # one NaN among ordinary values
+    x[10, 32:64] = float("nan")                 # a block of NaNs only (amax falls to the floor)
+    x[10, 70] = float("nan")
+    x[10, 71] = 300.0
+    x[11, 0] = float("inf")                     # an Inf among ordinary values
+    x[11, 40] = float("-inf")
+    x[11, 64:96] = float("inf")
+    x[12, 5] = float("nan")                     # NaN and Inf in the same block
+    x[12, 6] = float("-inf")
+    x[12, 200] = float("nan")
+    x[12, 255] = float("inf")
     return x.to(torch.bfloat16)
 
 
@@ -99,3 +112,7 @@ def to_np_u8(t: torch.Tensor) -> np.ndarray:
 
 def to_np_u32(t: torch.Tensor) -> np.ndarray:
     return t.detach().cpu().contiguous().numpy().view(np.uint32)
+
+
+GOLDEN = __import__("os").path.join(__import__("os").path.dirname(__import__("os").path.abspath(__file__)), "golden",
+                                    "quantize_1x32.npz")

@@ -63,8 +63,19 @@ def _worker(rank, world, port, ret):
                                                transport="peer")
         again = parallel.expert_parallel_layer(hidden, experts, ids, wts, num_experts_global=E)
         coll = parallel.expert_parallel_layer(hidden, experts, ids, wts, num_experts_global=E, transport="collective")
+        # several layers back to back with different routings and token counts (the receive buffers and the fences are
+        # reused from call to call): the peer transport must give the collective transport's bytes every time
+        rounds = []
+        for r in range(4):
+            t_r = 64 + 57 * r + 16 * rank
+            h_r = inputs.activation(t_r, H, 300 + 10 * r + rank).cuda()
+            ids_r, w_r = inputs.routing(t_r, E, K, 400 + 10 * r + rank, skew=1.2 if r % 2 else 0.0)
+            ids_r, w_r = ids_r.cuda(), w_r.cuda()
+            a = parallel.expert_parallel_layer(h_r, experts, ids_r, w_r, num_experts_global=E, transport="peer")
+            b = parallel.expert_parallel_layer(h_r, experts, ids_r, w_r, num_experts_global=E, transport="collective")
+            rounds.append(bool(torch.equal(a, b)))
         torch.cuda.synchronize()
-        ret[rank] = (y_part.cpu(), out.cpu(), _ops.device_status(), again.cpu(), coll.cpu(), other.cpu())
+        ret[rank] = (y_part.cpu(), out.cpu(), _ops.device_status(), again.cpu(), coll.cpu(), other.cpu(), rounds)
     finally:
         dist.destroy_process_group()
 
@@ -94,3 +105,4 @@ def test_n_split_and_expert_parallel_on_two_gpus(fso, oracle):
         assert torch.equal(ret[rank][1].view(torch.int16), ret[rank][3].view(torch.int16))
         assert torch.equal(ret[rank][1].view(torch.int16), ret[rank][4].view(torch.int16))
         assert not torch.equal(ret[rank][1].view(torch.int16), ret[rank][5].view(torch.int16))
+        assert ret[rank][6] == [True] * 4, ret[rank][6]

@@ -52,7 +52,8 @@ def test_known_bytes_of_the_rule(oracle):
 def test_integer_rule_equals_divide_rule_for_every_bf16_amax(oracle):
     L = oracle.lib()
     floor = np.float32(1e-10)
-    vals = [floor] + [v for v in (np.arange(1, 0x7F80, dtype=np.uint32) << 16).view(np.float32) if v >= floor]
+    # every bf16 magnitude from the floor up to and including +Inf (0x7F80)
+    vals = [floor] + [v for v in (np.arange(1, 0x7F81, dtype=np.uint32) << 16).view(np.float32) if v >= floor]
     for v in vals:
         a, b = ctypes.c_float(), ctypes.c_float()
         x = L.orc_e8m0_from_amax(ctypes.c_float(v), ctypes.byref(a))
@@ -183,3 +184,57 @@ def test_dense_epilogue_oracle_known_answers(oracle):
     assert torch.equal(oracle.dense_epilogue(acc, None, res, None), acc + res.float())
     with pytest.raises(ValueError):
         oracle.dense_epilogue(acc, None, None, "gelu_tanh")
+
+
+_CONTRACT_SHIM = r"""
+#include "fso_b200_activation_contract.h"
+void shim_quantize(const uint16_t* x, int64_t m, int64_t k, uint8_t* q, uint32_t* sf)
+{
+    int64_t const words = fso_b200_sf_words(m, k);
+    for (int64_t i = 0; i < words; ++i) sf[i] = 0;
+    for (int64_t r = 0; r < m; ++r)
+        for (int64_t kp = 0; kp < k / FSO_B200_CHUNK; ++kp) {
+            uint8_t b[4];
+            for (int j = 0; j < 4; ++j) {
+                float v[FSO_B200_BLOCK];
+                for (int i = 0; i < FSO_B200_BLOCK; ++i)
+                    v[i] = fso_b200_float_of((uint32_t)x[r * k + kp * FSO_B200_CHUNK + j * FSO_B200_BLOCK + i] << 16);
+                b[j] = fso_b200_quantize_block(v, q + r * k + kp * FSO_B200_CHUNK + j * FSO_B200_BLOCK);
+            }
+            sf[fso_b200_sf_word_index(r, kp, k)] = fso_b200_pack_word(b[0], b[1], b[2], b[3]);
+        }
+}
+"""
+
+
+def test_shipped_contract_header_gives_the_golden_bytes(oracle, tmp_path):
+    """include/fso_b200_activation_contract.h (what include_dir() hands a producer of pre-quantized activations),
+    compiled as plain C on the host, reproduces the reference header's bytes on the corner-case activation (NaN and
+    Inf rows included) and the oracle's on a random one."""
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "shim.c"
+    src.write_text(_CONTRACT_SHIM)
+    so = tmp_path / "shim.so"
+    subprocess.run(["gcc", "-std=c99", "-O2", "-ffp-contract=off", "-shared", "-fPIC", "-Wall", "-Werror",
+                    "-I", os.path.join(root, "include"), str(src), "-o", str(so)], check=True)
+    L = ctypes.CDLL(str(so))
+
+    def run(x):
+        xb = oracle.bf16_bits(x)
+        m, k = xb.shape
+        q = np.empty((m, k), np.uint8)
+        sf = np.empty(oracle.sf_words(m, k), np.uint32)
+        L.shim_quantize(xb.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(m), ctypes.c_int64(k),
+                        q.ctypes.data_as(ctypes.c_void_p), sf.ctypes.data_as(ctypes.c_void_p))
+        return q, sf
+
+    g = np.load(GOLDEN)
+    q, sf = run(inputs.edge_activation())
+    assert np.array_equal(q, g["edge_q"]) and np.array_equal(sf, g["edge_sf"])
+    x = (inputs.activation(300, 384, 77).float() * torch.exp2(torch.randint(-30, 30, (300, 1), generator=inputs.gen(78))
+                                                              .float())).to(torch.bfloat16)
+    q, sf = run(x)
+    oq, osf = oracle.quantize_1x32(x)
+    assert np.array_equal(q, oq) and np.array_equal(sf, osf)
