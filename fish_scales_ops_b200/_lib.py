@@ -35,6 +35,9 @@ SIGNATURES = {
     "fso_gemm_mxfp8_epilogue": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_i64, _c_p, _c_i64,
                                 _c_p],
     "fso_quantize_activation_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_p],
+    "fso_gemm_mxfp8_fuses_quantized_output": [_c_i64, _c_i64, _c_i64, ctypes.POINTER(ctypes.c_int)],
+    "fso_gemm_mxfp8_quantized": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_i64, _c_p],
+    "fso_gemm_mxfp8_swiglu": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
     "fso_stream_fence": [_c_p],
     "fso_silu_mul_quantize_1x32": [_c_p, _c_p, _c_p, _c_i64, _c_i64, _c_p],
     "fso_moe_topk_from_logits": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p,

@@ -132,6 +132,51 @@ def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.
     return out
 
 
+_FUSES_QUANT = {}
+
+
+def gemm_fuses_quantized_output(m: int, n: int, k: int) -> bool:
+    """Whether this shape's GEMM can emit the activation contract itself (a pure function of the shape and the
+    device's SM count; cached)."""
+    key = (m, n, k, torch.cuda.current_device())
+    if key not in _FUSES_QUANT:
+        v = ctypes.c_int(0)
+        check(lib().fso_gemm_mxfp8_fuses_quantized_output(m, n, k, ctypes.byref(v)), "fso_gemm_mxfp8_fuses_quantized_output")
+        _FUSES_QUANT[key] = bool(v.value)
+    return _FUSES_QUANT[key]
+
+
+def linear_mxfp8_quantized(xq, w, sx, sw, bias=None, activation: int = 0):
+    """(float8_e4m3fn [M, N], int32 scale words) = quantize_activation(linear_mxfp8(...)), bit for bit; one launch
+    where the shape allows, otherwise the GEMM followed by the activation quantizer."""
+    m, k = int(xq.shape[0]), int(xq.shape[1])
+    n = int(w.shape[0])
+    with torch.cuda.device(xq.device):
+        if m > 0 and gemm_fuses_quantized_output(m, n, k):
+            out = torch.empty((m, n), dtype=FP8, device=xq.device)
+            sf = torch.empty((sf_words(m, n),), dtype=torch.int32, device=xq.device)
+            check(lib().fso_gemm_mxfp8_quantized(ptr(xq), ptr(sx), ptr(w), ptr(sw), ptr(out), ptr(sf), m, n, k, ptr(bias),
+                                                 int(activation), stream_ptr()), "fso_gemm_mxfp8_quantized")
+            return out, sf
+    y = linear_mxfp8(xq, w, sx, sw, bias, None, activation)
+    return quantize_1x32_fp8(y, activation=True)
+
+
+def linear_mxfp8_swiglu(xq, w_interleaved, sx, sw):
+    """silu(gate) * up of the gate_up projection as (float8_e4m3fn [M, I], int32 scale words), one launch;
+    ``w_interleaved`` e4m3 [2I, K] with gate_j / up_j in rows 2j / 2j+1."""
+    m, k = int(xq.shape[0]), int(xq.shape[1])
+    two_i = int(w_interleaved.shape[0])
+    inter = two_i // 2
+    with torch.cuda.device(xq.device):
+        dq = torch.empty((m, inter), dtype=FP8, device=xq.device)
+        sd = torch.empty((sf_words(m, inter),), dtype=torch.int32, device=xq.device)
+        if m > 0:
+            check(lib().fso_gemm_mxfp8_swiglu(ptr(xq), ptr(sx), ptr(w_interleaved), ptr(sw), ptr(dq), ptr(sd), m, two_i,
+                                              k, stream_ptr()), "fso_gemm_mxfp8_swiglu")
+    return dq, sd
+
+
 def moe_plan(tokens: int, topk: int, num_experts: int) -> MoePlan:
     p = MoePlan()
     check(lib().fso_moe_plan_make(tokens, topk, num_experts, ctypes.byref(p)), "fso_moe_plan_make")

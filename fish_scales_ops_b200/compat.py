@@ -9,7 +9,8 @@ import torch
 from . import _ops
 from ._arch import SERVED_MAJOR, arch_label, device_arch
 
-__all__ = ["moe_topk_from_logits", "moe_router_topk", "silu_chunk_mul_quantize_1x32_fp8"]
+__all__ = ["moe_topk_from_logits", "moe_router_topk", "silu_chunk_mul_quantize_1x32_fp8", "prepare_gate_up",
+           "linear_swiglu"]
 
 _MAX_EXPERTS = 1024
 _MAX_TOPK = 8
@@ -121,3 +122,93 @@ def silu_chunk_mul_quantize_1x32_fp8(gu: torch.Tensor) -> Tuple[torch.Tensor, to
     reaching memory."""
     two_i = int(gu.shape[-1])
     return torch.ops.fish_scales_ops.silu_chunk_mul_quantize_1x32(gu.reshape(-1, two_i), True)
+
+
+# ------------------------------------------------------------------------------------------ dense SwiGLU, fused
+
+def prepare_gate_up(w: torch.Tensor, *, format: str = "mxfp8", scale: Optional[torch.Tensor] = None):
+    """Prepare the stacked gate_up weight ``[2*INTER, K]`` (gate rows first, as checkpoints store it) of a dense SwiGLU
+    MLP for :func:`linear_swiglu`: MXFP8 with the rows interleaved (gate_j, up_j adjacent), the order the fused
+    epilogue reads, which is the order ``fso.moe.prepare_experts`` gives the experts' FC1 weights
+    (python/fish_scales_ops/gemm/mxfp8.py:621-633). ``format="mxfp8"`` takes a bf16 weight, ``format="bsfp8"`` a
+    float8_e4m3fn weight with its fp32 ``[2*INTER/128, K/128]`` block scales. Returns a ``DenseWeight``; hand it to
+    :func:`linear_swiglu` only (``fso.dense.linear`` on it would give the columns in interleaved order)."""
+    from . import dense
+
+    arch = device_arch()
+    ctx = f"fso.compat.prepare_gate_up (format {format!r}, {arch_label(arch)})"
+    if arch // 10 != SERVED_MAJOR:
+        raise NotImplementedError(f"{ctx}: this build serves sm_100-family devices")
+    if not isinstance(w, torch.Tensor) or w.dim() != 2 or not w.is_cuda:
+        raise ValueError(f"{ctx}: w must be a CUDA [2*INTER, K] tensor")
+    two_i, k = int(w.shape[0]), int(w.shape[1])
+    if two_i % 256 != 0 or k % 128 != 0:
+        raise ValueError(f"{ctx}: 2*INTER = {two_i} must be a multiple of 256 and K = {k} a multiple of 128")
+    if format == "mxfp8":
+        if w.dtype != torch.bfloat16 or scale is not None:
+            raise ValueError(f"{ctx}: takes a bf16 weight and no scale")
+        q, sq = _ops.quantize_1x32_fp8(w.detach(), interleave_i=two_i // 2)
+    elif format == "bsfp8":
+        if w.dtype != torch.float8_e4m3fn or not isinstance(scale, torch.Tensor) or scale.dtype != torch.float32 \
+                or tuple(scale.shape) != (two_i // 128, k // 128) or (two_i // 2) % 128 != 0:
+            raise ValueError(f"{ctx}: takes a float8_e4m3fn weight with fp32 [{two_i // 128}, {k // 128}] block scales "
+                             f"and INTER a multiple of 128")
+        q, sq = _ops.requant_block_fp8(w.detach().contiguous(), scale.detach().contiguous(), interleave_i=two_i // 2)
+    else:
+        raise ValueError(f"{ctx}: the formats are 'mxfp8' and 'bsfp8'")
+    _ops.stream_fence(w.device)
+    return dense.DenseWeight("mxfp8", format, arch, k, two_i, q, sq)
+
+
+@torch.library.custom_op(
+    "fish_scales_ops::dense_linear_swiglu",
+    mutates_args=(),
+    schema="(Tensor x, Tensor weight, Tensor scale, Tensor? x_scale=None) -> (Tensor, Tensor)",
+)
+def _dense_linear_swiglu_op(x, weight, scale, x_scale=None):
+    op = f"fish_scales_ops::dense_linear_swiglu ({arch_label(device_arch())})"
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
+        raise ValueError(f"{op}: x must be [M, K] and weight [2*INTER, K] with the same K, got {tuple(x.shape)} and "
+                         f"{tuple(weight.shape)}")
+    two_i, k = int(weight.shape[0]), int(weight.shape[1])
+    if weight.dtype != torch.float8_e4m3fn or two_i % 256 != 0 or k % 128 != 0 or not weight.is_contiguous():
+        raise ValueError(f"{op}: weight must be a contiguous float8_e4m3fn [2*INTER, K] with 2*INTER % 256 == 0")
+    if scale.dtype != torch.int32 or scale.dim() != 1 or scale.numel() != two_i * (k // 128):
+        raise ValueError(f"{op}: scale must be the 1-D int32 atom-layout scale of the weight")
+    m = int(x.shape[0])
+    if x_scale is None:
+        if x.dtype != torch.bfloat16:
+            raise ValueError(f"{op}: x must be bf16 (or float8_e4m3fn with x_scale), got {x.dtype}")
+        if m > 0 and (not x.is_contiguous() or x.data_ptr() % 16 != 0):
+            x = x.contiguous() if not x.is_contiguous() else x.clone()
+        x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
+    else:
+        if x.dtype != torch.float8_e4m3fn or not x.is_contiguous() or (m > 0 and x.data_ptr() % 16 != 0):
+            raise ValueError(f"{op}: with x_scale, x must be the contiguous, 16-byte aligned float8_e4m3fn activation")
+        if x_scale.dtype != torch.int32 or x_scale.dim() != 1 or x_scale.numel() != _ops.sf_words(m, k):
+            raise ValueError(f"{op}: x_scale must be the int32 [{_ops.sf_words(m, k)}] scale of an [M, K] activation")
+    return _ops.linear_mxfp8_swiglu(x, weight, x_scale, scale)
+
+
+@_dense_linear_swiglu_op.register_fake
+def _dense_linear_swiglu_fake(x, weight, scale, x_scale=None):
+    m, inter = x.shape[0], weight.shape[0] // 2
+    return (x.new_empty((m, inter), dtype=torch.float8_e4m3fn),
+            x.new_empty(((m + 127) // 128 * 128 * (inter // 128),), dtype=torch.int32))
+
+
+def linear_swiglu(x: torch.Tensor, gate_up, *, x_scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``silu(x W_gate^T) * (x W_up^T)`` of a dense SwiGLU MLP in ONE launch, returned in the activation contract
+    ``(float8_e4m3fn [M, INTER], int32 scale words)`` ready for ``fso.dense.linear(hq, down, x_scale=hs)``: the gate_up
+    GEMM with the activation and the 1x32 quantization in its epilogue (fp32 accumulators, hardware tanh), so the bf16
+    ``[M, 2*INTER]`` product never reaches memory. ``gate_up`` is the handle of :func:`prepare_gate_up`. The two-kernel
+    form it replaces is ``silu_chunk_mul_quantize_1x32_fp8(fso.dense.linear(x, gate_up_plain))``
+    (python/fish_scales_ops/gemm/mxfp8.py:216-236)."""
+    from . import dense
+
+    if not isinstance(gate_up, dense.DenseWeight):
+        raise TypeError(f"fso.compat.linear_swiglu: gate_up must be the handle of fso.compat.prepare_gate_up, got "
+                        f"{type(gate_up).__name__}")
+    k = gate_up.in_features
+    x2 = x if x_scale is not None else x.reshape(-1, k)
+    return torch.ops.fish_scales_ops.dense_linear_swiglu(x2, gate_up.weight, gate_up.scale, x_scale)

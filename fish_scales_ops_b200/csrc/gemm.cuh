@@ -27,13 +27,16 @@ namespace fso {
 // slices of one tile; slices 1.. store their fp32 accumulators into CTA 0's shared memory (distributed shared memory),
 // CTA 0 adds them in slice order and writes bf16: the same sums as EPI_PARTIAL + splitk_reduce_kernel, in one launch
 // and without a workspace.
-enum : int { EPI_BF16 = 0, EPI_PARTIAL = 1, EPI_SWIGLU = 2, EPI_CLUSTER = 3 };
+// EPI_QUANT (normal orientation): the output leaves in the activation contract instead of bf16: per row and 32
+// output columns act(acc + bias) is rounded to bf16 (so that the bytes equal quantizing the bf16 output afterwards),
+// then amax -> UE8M0 byte -> e4m3 codes; `out` is e4m3 [M, N], `out_sf` its scale words.
+enum : int { EPI_BF16 = 0, EPI_PARTIAL = 1, EPI_SWIGLU = 2, EPI_CLUSTER = 3, EPI_QUANT = 4 };
 
 struct GemmParams {
     const uint8_t* sfa;        // scale words of the operand on MMA-M
     const uint8_t* sfb;        // scale words of the operand on MMA-N
-    void* out;                 // bf16 [M, N]; EPI_SWIGLU: e4m3 [rows, I]
-    uint32_t* out_sf;          // EPI_SWIGLU: scale words of the [rows, I] output
+    void* out;                 // bf16 [M, N]; EPI_SWIGLU: e4m3 [rows, I]; EPI_QUANT: e4m3 [M, N]
+    uint32_t* out_sf;          // EPI_SWIGLU / EPI_QUANT: scale words of the e4m3 output
     float* ws;                 // EPI_PARTIAL: fp32 [splits, M, N]
     const int32_t* blk0;       // grouped: blk0[num_experts] = blocks in use
     const int32_t* blk_expert; // grouped: expert of each 128-row block
@@ -442,6 +445,10 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     // byte `half` (0..3) of the row's scale word for K block b_tile of the output
                     reinterpret_cast<uint8_t*>(p.out_sf)[sf_word_index(a_row, c.b_tile, inter / 128) * 4 + half]
                         = static_cast<uint8_t>(byte);
+                } else if constexpr (!kGrouped) {
+                    // dense call: the rows between M and the next multiple of 128 carry zero scale words, as every
+                    // producer of the activation contract leaves them
+                    reinterpret_cast<uint8_t*>(p.out_sf)[sf_word_index(a_row, c.b_tile, inter / 128) * 4 + half] = 0;
                 }
             } else if constexpr (!kSwap && EPI == EPI_BF16) {
                 // row = output row, columns = output columns. The accumulator slice is drained into packed bf16
@@ -523,6 +530,83 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             }
                         }
                     }
+                }
+            } else if constexpr (!kSwap && EPI == EPI_QUANT) {
+                // row = output row; per 32 columns one 1x32 block of the next layer's activation
+                static_assert(kColsPerWarp == 128 || kColsPerWarp == 64, "whole or half scale words per warp");
+                uint32_t codes[kColsPerWarp / 4];
+                uint32_t word = 0;
+                int const col_w = b_row0 + half * kColsPerWarp;          // first output column of this warp
+#pragma unroll
+                for (int c0 = 0; c0 < kColsPerWarp; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + half * kColsPerWarp + c0, r);
+                    tmem_ld_wait();
+                    if constexpr (kFused) {
+                        if (col_w + c0 < p.rows_b) {
+                            bool const has_bias = p.bias != nullptr;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint4 bw = make_uint4(0, 0, 0, 0);
+                                if (has_bias) bw = __ldg(reinterpret_cast<const uint4*>(p.bias + col_w + c0 + 8 * q));
+                                uint32_t const bws[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    r[8 * q + 2 * i] = __float_as_uint(epilogue_value(__uint_as_float(r[8 * q + 2 * i]),
+                                        bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] & 0xFFFFu))),
+                                        has_bias, p.act));
+                                    r[8 * q + 2 * i + 1] = __float_as_uint(epilogue_value(
+                                        __uint_as_float(r[8 * q + 2 * i + 1]),
+                                        bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] >> 16))),
+                                        has_bias, p.act));
+                                }
+                            }
+                        }
+                    }
+                    float v[32];
+                    float amax = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));   // the bf16 output's value
+                        amax = fmaxf(amax, fabsf(v[j]));
+                    }
+                    amax = fmaxf(amax, 1e-10f);
+                    float qs;
+                    word |= e8m0_from_amax(amax, qs) << (8 * (c0 / 32));
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        codes[c0 / 4 + q] = fp8x4(__fmul_rn(v[4 * q], qs), __fmul_rn(v[4 * q + 1], qs),
+                            __fmul_rn(v[4 * q + 2], qs), __fmul_rn(v[4 * q + 3], qs));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                released = true;
+                if (col_w < p.rows_b) {
+                    int const kp = col_w >> 7;
+                    uint8_t* const sfb = reinterpret_cast<uint8_t*>(p.out_sf) + sf_word_index(a_row, kp, p.ldo / 128) * 4;
+                    if (a_row < p.rows_a) {
+                        uint8_t* const dst = static_cast<uint8_t*>(p.out) + static_cast<int64_t>(a_row) * p.ldo + col_w;
+#pragma unroll
+                        for (int c0 = 0; c0 < kColsPerWarp; c0 += 32) {
+                            uint32_t const* o = &codes[c0 / 4];
+                            if (p.out_align32) {
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                             ::"l"(dst + c0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]),
+                                             "r"(o[5]), "r"(o[6]), "r"(o[7])
+                                             : "memory");
+                            } else {
+                                reinterpret_cast<uint4*>(dst + c0)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                                reinterpret_cast<uint4*>(dst + c0)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                            }
+                        }
+                    } else {
+                        word = 0;                        // rows between M and the next multiple of 128: zero words
+                    }
+                    if constexpr (kColsPerWarp == 128)
+                        *reinterpret_cast<uint32_t*>(sfb) = word;
+                    else
+                        *reinterpret_cast<uint16_t*>(sfb + ((col_w & 127) >> 5)) = static_cast<uint16_t>(word);
                 }
             } else if constexpr (!kSwap) {
                 // split-K partial, normal orientation: fp32 rows straight from tensor memory

@@ -364,8 +364,17 @@ struct DenseEpi {
     const void* bias = nullptr;
     const void* residual = nullptr;
     int act = 0;
+    void* quant_sf = nullptr;        // set: the output leaves as e4m3 codes (d) + these scale words (EPI_QUANT)
     bool any() const { return bias != nullptr || residual != nullptr || act != 0; }
 };
+
+// The quantizing epilogue serves the shapes that run in the normal orientation without split-K (every other shape
+// computes bf16 first and runs the activation quantizer behind it, which gives the same bytes).
+inline bool dense_fuses_quantized_output(int64_t m, int64_t n, int64_t k, int sms)
+{
+    DensePlan const pl = plan_dense(m, n, k, sms);
+    return !pl.swap && pl.splits == 1;
+}
 
 inline int launch_dense(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
     int64_t k, void* ws, int64_t ws_bytes, cudaStream_t stream, DenseEpi epi = DenseEpi{})
@@ -379,7 +388,15 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
         return FSO_ERR_INVALID;
     }
     bool const fused = epi.any();
-    if (!fused && use_pair_kernel(m, n, sms, pl.swap, pl.splits)) return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
+    bool const quant = epi.quant_sf != nullptr;
+    if (quant && (pl.swap || pl.splits != 1)) {
+        set_error("fso_gemm_mxfp8_quantized: M = %lld, N = %lld, K = %lld does not take the fused form "
+                  "(fso_gemm_mxfp8_fuses_quantized_output)", static_cast<long long>(m), static_cast<long long>(n),
+            static_cast<long long>(k));
+        return FSO_ERR_UNSUPPORTED;
+    }
+    if (!fused && !quant && use_pair_kernel(m, n, sms, pl.swap, pl.splits))
+        return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
     CUtensorMap ta, tb;
     GemmParams p{};
     p.kb_total = static_cast<int>(k / 128);
@@ -390,6 +407,7 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     p.group_a = pl.group_a;
     p.ldo = static_cast<int>(n);
     p.out = d;
+    p.out_sf = static_cast<uint32_t*>(epi.quant_sf);
     p.ws = static_cast<float*>(ws);
     p.out_rows = m;
     p.out_align32 = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 ? 1 : 0;
@@ -445,6 +463,13 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
                           : launch_gemm_cluster<64>(ta, tb, p, static_cast<int>(items), stream);
     }
     bool const partial = splits > 1;
+    if (quant) {
+        if (pl.bn == 256)
+            return fused ? launch_gemm_inst<256, EPI_QUANT, false, false, true>(ta, tb, p, grid, stream)
+                         : launch_gemm_inst<256, EPI_QUANT, false, false>(ta, tb, p, grid, stream);
+        return fused ? launch_gemm_inst<128, EPI_QUANT, false, false, true>(ta, tb, p, grid, stream)
+                     : launch_gemm_inst<128, EPI_QUANT, false, false>(ta, tb, p, grid, stream);
+    }
 #define FSO_DENSE_CASE(BN_, SWAP_)                                                                                 \
     if (pl.bn == BN_ && pl.swap == SWAP_) {                                                                        \
         rc = partial ? launch_gemm_inst<BN_, EPI_PARTIAL, SWAP_, false>(ta, tb, p, grid, stream)                   \
@@ -476,6 +501,38 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
         rc = launch_status("splitk_reduce_kernel");
     }
     return rc;
+}
+
+// The gate_up projection of a dense SwiGLU MLP with the activation fused: w is [2I, K] with its rows interleaved
+// (gate_j, up_j adjacent), out = silu(gate) * up as e4m3 [M, I] + scale words: the grouped FC1 epilogue on a dense
+// operand. Always the normal orientation (the epilogue needs a row's gate / up pairs in one thread).
+inline int launch_dense_swiglu(const void* a, const void* sfa, const void* w, const void* sfw, void* dq, void* sd,
+    int64_t m, int64_t two_i, int64_t k, cudaStream_t stream)
+{
+    int const sms = sm_count();
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_operand_map(&ta, a, m, k, 128)) != 0) return rc;
+    if ((rc = make_operand_map(&tb, w, two_i, k, 256)) != 0) return rc;
+    GemmParams p{};
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb = static_cast<const uint8_t*>(sfw);
+    p.out = dq;
+    p.out_sf = static_cast<uint32_t*>(sd);
+    p.rows_a = static_cast<int>(m);
+    p.rows_b = static_cast<int>(two_i);
+    p.kb_total = static_cast<int>(k / 128);
+    p.kb_per_split = p.kb_total;
+    p.splits = 1;
+    p.tiles_a = static_cast<int>((m + 127) / 128);
+    p.tiles_b = static_cast<int>(two_i / 256);
+    p.ldo = static_cast<int>(two_i / 2);
+    p.group_a = p.tiles_a < 16 ? p.tiles_a : 16;
+    p.out_rows = m;
+    p.out_align32 = (reinterpret_cast<uintptr_t>(dq) & 31u) == 0 ? 1 : 0;
+    int64_t const items = static_cast<int64_t>(p.tiles_a) * p.tiles_b;
+    int const grid = static_cast<int>(items < sms ? items : sms);
+    return launch_gemm_inst<256, EPI_SWIGLU, false, false>(ta, tb, p, grid, stream);
 }
 
 // Grouped GEMM over the compact activation: block b (rows [128b, 128b+128) of `a`) times weight[blk_expert[b]]^T.

@@ -214,6 +214,50 @@ int fso_gemm_mxfp8_epilogue(const void* a, const void* sfa, const void* w, const
     return launch_dense(a, sfa, w, sfw, d, m, n, k, ws, ws_bytes, as_stream(stream), epi);
 }
 
+int fso_gemm_mxfp8_fuses_quantized_output(int64_t m, int64_t n, int64_t k, int* yes)
+{
+    FSO_REQUIRE(yes != nullptr, "fso_gemm_mxfp8_fuses_quantized_output: yes is NULL");
+    int const rc = check_gemm_shape("fso_gemm_mxfp8_fuses_quantized_output", m, n, k);
+    if (rc != 0) return rc;
+    *yes = (m > 0 && dense_fuses_quantized_output(m, n, k, sm_count())) ? 1 : 0;
+    return 0;
+}
+
+int fso_gemm_mxfp8_quantized(const void* a, const void* sfa, const void* w, const void* sfw, void* out_q, void* out_sf,
+    int64_t m, int64_t n, int64_t k, const void* bias, int64_t activation, void* stream)
+{
+    int const rc = check_gemm_shape("fso_gemm_mxfp8_quantized", m, n, k);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(activation == 0 || activation == 1,
+        "fso_gemm_mxfp8_quantized: activation must be 0 (identity) or 1 (erf-GELU), got %lld",
+        static_cast<long long>(activation));
+    if (m == 0) return 0;
+    FSO_REQUIRE(a && sfa && w && sfw && out_q && out_sf, "fso_gemm_mxfp8_quantized: NULL pointer");
+    FSO_REQUIRE(aligned16(a) && aligned16(sfa) && aligned16(w) && aligned16(sfw) && aligned16(out_q)
+            && (reinterpret_cast<uintptr_t>(out_sf) & 3u) == 0 && (bias == nullptr || aligned16(bias)),
+        "fso_gemm_mxfp8_quantized: operands, out_q and bias must be 16-byte aligned, out_sf 4-byte aligned");
+    DenseEpi epi;
+    epi.bias = bias;
+    epi.act = static_cast<int>(activation);
+    epi.quant_sf = out_sf;
+    return launch_dense(a, sfa, w, sfw, out_q, m, n, k, nullptr, 0, as_stream(stream), epi);
+}
+
+int fso_gemm_mxfp8_swiglu(const void* a, const void* sfa, const void* w, const void* sfw, void* dq, void* sd, int64_t m,
+    int64_t two_i, int64_t k, void* stream)
+{
+    int const rc = check_gemm_shape("fso_gemm_mxfp8_swiglu", m, two_i, k);
+    if (rc != 0) return rc;
+    FSO_REQUIRE(two_i % 256 == 0, "fso_gemm_mxfp8_swiglu: 2*I = %lld must be a multiple of 256",
+        static_cast<long long>(two_i));
+    if (m == 0) return 0;
+    FSO_REQUIRE(a && sfa && w && sfw && dq && sd, "fso_gemm_mxfp8_swiglu: NULL pointer");
+    FSO_REQUIRE(aligned16(a) && aligned16(sfa) && aligned16(w) && aligned16(sfw) && aligned16(dq)
+            && (reinterpret_cast<uintptr_t>(sd) & 3u) == 0,
+        "fso_gemm_mxfp8_swiglu: operands and dq must be 16-byte aligned, sd 4-byte aligned");
+    return launch_dense_swiglu(a, sfa, w, sfw, dq, sd, m, two_i, k, as_stream(stream));
+}
+
 int fso_moe_plan_make(int64_t tokens, int64_t topk, int64_t num_experts, fso_moe_plan* plan)
 {
     FSO_REQUIRE(plan != nullptr, "fso_moe_plan_make: plan is NULL");

@@ -420,8 +420,9 @@ def _dense_linear_fake(x, weight, scale, kind, bias=None, x_scale=None, residual
 )
 def _dense_linear_quantized_op(x, weight, scale, kind, bias=None, x_scale=None, activation=None):
     """Body of ``torch.ops.fish_scales_ops.dense_linear_quantized``: the result of ``dense_linear`` in the
-    activation contract. Here it is the GEMM followed by the activation quantizer, which is the definition the
-    reference states for it (python/fish_scales_ops/dense/__init__.py:1212-1241)."""
+    activation contract (python/fish_scales_ops/dense/__init__.py:1212-1241). For the shapes the GEMM serves in its
+    normal orientation without split-K the quantization happens in the GEMM's epilogue (one launch, no bf16 round
+    trip); for the others it is the GEMM followed by the activation quantizer. Both give the same bytes."""
     op = f"fish_scales_ops::dense_linear_quantized ({arch_label(device_arch())}, kind {kind!r})"
     _check_operands(op, x, weight, x_scale)
     m, n, k = int(x.shape[0]), int(weight.shape[0]), int(x.shape[1])
@@ -439,8 +440,7 @@ def _dense_linear_quantized_op(x, weight, scale, kind, bias=None, x_scale=None, 
     bias, _ = _epilogue_storage(op, bias, None)
     if x_scale is None:
         x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
-    y = _ops.linear_mxfp8(x, weight, x_scale, scale, bias, None, 1 if activation == "gelu_erf" else 0)
-    return _ops.quantize_1x32_fp8(y, activation=True)
+    return _ops.linear_mxfp8_quantized(x, weight, x_scale, scale, bias, 1 if activation == "gelu_erf" else 0)
 
 
 @_dense_linear_quantized_op.register_fake

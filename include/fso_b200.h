@@ -104,6 +104,28 @@ int fso_gemm_mxfp8_epilogue(const void* a, const void* sfa, const void* w, const
                             int64_t n, int64_t k, const void* bias, const void* residual, int64_t activation,
                             void* ws, int64_t ws_bytes, void* stream);
 
+/* The same GEMM with its output in the activation contract instead of bf16: out_q e4m3 [M, N] and out_sf the scale
+ * words of an [M, N] activation (align(M,128) * N/128 words, rows past M zero), bit for bit what
+ * fso_quantize_activation_1x32 gives on the bf16 output of fso_gemm_mxfp8_epilogue(bias, activation): the epilogue
+ * rounds act(acc + bias) to bf16 first and then applies the 1x32 rule per row and 32 columns, one launch and no
+ * bf16 round trip through memory. Served for the shapes fso_gemm_mxfp8_fuses_quantized_output answers 1 for (normal
+ * orientation, no split-K); FSO_ERR_UNSUPPORTED otherwise, and the caller runs the two launches.
+ * Replaces: op linear_mxfp8_quantized_raw and its epilogue, csrc/gemm/include/blockscale_gemm/common/epilogue.cuh:14,
+ * 47-57, arch/sm100/mxfp8/dense_epi_math.cuh:203-214; python/fish_scales_ops/dense/__init__.py:1004-1047. */
+int fso_gemm_mxfp8_fuses_quantized_output(int64_t m, int64_t n, int64_t k, int* yes);
+int fso_gemm_mxfp8_quantized(const void* a, const void* sfa, const void* w, const void* sfw, void* out_q, void* out_sf,
+    int64_t m, int64_t n, int64_t k, const void* bias, int64_t activation, void* stream);
+
+/* The gate_up projection of a dense SwiGLU MLP with the activation fused into the GEMM: w e4m3 [2I, K] with its rows
+ * interleaved (gate_j, up_j adjacent; fso_quantize_1x32 / fso_requant_bs128_to_mx with interleave_i = I produce
+ * that order), dq = silu(gate) * up as e4m3 [M, I], sd its scale words (align(M,128) * I/128, rows past M zero), ready
+ * to be the activation of the down projection. 2I % 256 == 0.
+ * Replaces the two-kernel chain linear_mxfp8 + silu_chunk_mul_quantize_1x32_fp8
+ * (python/fish_scales_ops/gemm/mxfp8.py:216-236, csrc/gemm/ops/quant_kernels.cu:690-727) by the dense form of the
+ * fused FC1 epilogue (csrc/gemm/include/blockscale_gemm/arch/sm100/mxfp8/fused_swiglu_store.cuh:266-346). */
+int fso_gemm_mxfp8_swiglu(const void* a, const void* sfa, const void* w, const void* sfw, void* dq, void* sd, int64_t m,
+    int64_t two_i, int64_t k, void* stream);
+
 /* Host-static sizes of one MoE layer call (functions of the argument shapes only).
  * Replaces: _mxfp8_layer_plan / moe_compact_num_blocks, python/fish_scales_ops/gemm/mxfp8.py:1653-1728, 1228-1239. */
 typedef struct fso_moe_plan {

@@ -400,3 +400,27 @@ def test_dense_epilogue_against_torch_on_device(fso, device_ok):
     want = torch.nn.functional.gelu(base + bias.float()) + res.float()
     err = (y.float() - want).abs().max() / want.abs().max()
     assert float(err) < 2e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 1024, 512), (1024, 4096, 1024), (4096, 2048 + 128, 512), (129, 8192, 256)])
+def test_linear_quantized_fused_epilogue_equals_two_launches(fso, device_ok, m, n, k):
+    """For shapes the GEMM runs in its normal orientation without split-K, linear_quantized is one launch (the 1x32
+    quantization happens in the GEMM's epilogue, after the rounding to bf16) and gives exactly the bytes of
+    quantize_activation(linear(...)), with and without bias / activation; scale words of rows past M are zero."""
+    from fish_scales_ops_b200 import _ops
+
+    assert _ops.gemm_fuses_quantized_output(m, n, k)
+    x = inputs.activation(m, k, 11).cuda()
+    weight = fso.dense.prepare_weight(inputs.weight(n, k, 12).cuda(), format="mxfp8")
+    bias = (0.5 * torch.randn(n, generator=inputs.gen(13))).to(torch.bfloat16).cuda()
+    for kw in ({}, {"bias": bias}, {"activation": "gelu_erf"}, {"bias": bias, "activation": "gelu_erf"}):
+        yq, ys = fso.dense.linear_quantized(x, weight, **kw)
+        want_q, want_s = fso.dense.quantize_activation(fso.dense.linear(x, weight, **kw))
+        assert yq.dtype == torch.float8_e4m3fn and tuple(yq.shape) == (m, n)
+        assert torch.equal(yq.view(torch.uint8), want_q.view(torch.uint8)), kw
+        assert torch.equal(ys, want_s), kw
+    # small M takes the swapped orientation: two launches, same contract
+    assert not _ops.gemm_fuses_quantized_output(16, n, k)
+    q16, s16 = fso.dense.linear_quantized(x[:16], weight)
+    w16q, w16s = fso.dense.quantize_activation(fso.dense.linear(x[:16], weight))
+    assert torch.equal(q16.view(torch.uint8), w16q.view(torch.uint8)) and torch.equal(s16, w16s)

@@ -64,6 +64,49 @@ def test_swiglu_mlp_chain(fso, oracle, device_ok, m):
     inputs.assert_close_to_oracle(y, hd @ wd.t(), f"SwiGLU MLP chain M={m}")
 
 
+@pytest.mark.parametrize("m,h,inter", [(16, 512, 1024), (300, 512, 1024), (1000, 1024, 2048)])
+def test_fused_swiglu_mlp_chain(fso, oracle, device_ok, m, h, inter):
+    """The same chain with the middle step inside the gate_up GEMM (fso.compat.linear_swiglu): two launches for the
+    MLP's two projections, no bf16 [M, 2I] tensor. Against the oracle's fp32 chain from the quantized operands (exact
+    silu on the fp32 accumulators, 1x32 rule, fp32 down projection); the intermediate against the oracle's by value,
+    and against the two-kernel form, which differs only by the bf16 rounding of gate_up it inserts."""
+    x = inputs.activation(m, h, 3)
+    w_gu_master = inputs.weight(2 * inter, h, 4)
+    w_gu = fso.compat.prepare_gate_up(w_gu_master.cuda(), format="mxfp8")
+    w_dn = fso.dense.prepare_weight(inputs.weight(h, inter, 5).cuda(), format="mxfp8")
+    # the handle holds the bytes of the interleaved weight
+    oq, osf = oracle.quantize_1x32(w_gu_master, interleave_i=inter)
+    assert np.array_equal(inputs.to_np_u8(w_gu.weight), oq) and np.array_equal(inputs.to_np_u32(w_gu.scale), osf)
+    hq, hs = fso.compat.linear_swiglu(x.cuda(), w_gu)
+    assert hq.dtype == torch.float8_e4m3fn and tuple(hq.shape) == (m, inter)
+    assert hs.numel() == (m + 127) // 128 * 128 * (inter // 128)
+    y = fso.dense.linear(hq, w_dn, x_scale=hs)
+    acc = oracle.dense_linear(x, oq, osf).numpy()                       # fp32 [M, 2I], columns gate_j, up_j adjacent
+    dq, sd = oracle.swiglu_quant(acc, np.ones(m, np.uint8))
+    hd = torch.from_numpy(oracle.dequant(dq, sd))
+    got = torch.from_numpy(oracle.dequant(inputs.to_np_u8(hq), inputs.to_np_u32(hs)))
+    assert inputs.rel_frobenius(got, hd) <= 2e-2
+    assert (inputs.to_np_u8(hq) == dq).mean() > 0.97
+    wd = torch.from_numpy(oracle.dequant(inputs.to_np_u8(w_dn.weight), inputs.to_np_u32(w_dn.scale)))
+    inputs.assert_close_to_oracle(y, hd @ wd.t(), f"fused SwiGLU MLP chain M={m}")
+    # scale words of the rows past M are zero
+    got_s = inputs.to_np_u32(hs)
+    kb = inter // 128
+    rows = np.arange(m, (m + 127) // 128 * 128)
+    if rows.size:
+        idx = oracle.sf_word_index(np.repeat(rows, kb), np.tile(np.arange(kb), rows.size), inter)
+        assert not got_s[idx].any()
+    # the two-kernel form on a plain (not interleaved) weight agrees by value
+    plain = fso.dense.prepare_weight(w_gu_master.cuda(), format="mxfp8")
+    q2, s2 = fso.compat.silu_chunk_mul_quantize_1x32_fp8(fso.dense.linear(x.cuda(), plain))
+    two = torch.from_numpy(oracle.dequant(inputs.to_np_u8(q2), inputs.to_np_u32(s2)))
+    assert inputs.rel_frobenius(got, two) <= 2e-2
+    # the pre-quantized entry gives the same bytes
+    xq, sx = fso.dense.quantize_activation(x.cuda())
+    hq3, hs3 = fso.compat.linear_swiglu(xq, w_gu, x_scale=sx)
+    assert torch.equal(hq3.view(torch.uint8), hq.view(torch.uint8)) and torch.equal(hs3, hs)
+
+
 def test_silu_mul_quantize_refusals(fso, device_ok):
     with pytest.raises(ValueError):
         fso.compat.silu_chunk_mul_quantize_1x32_fp8(torch.zeros(4, 200, dtype=torch.bfloat16, device="cuda"))
