@@ -31,6 +31,9 @@ SIGNATURES = {
     "fso_moe_fc1_swiglu": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p,
                            _c_p],
     "fso_moe_fc2": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p],
+    "fso_moe_grouped_gemm_decode": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64,
+                                    _c_p, _c_i64, _c_i64, _c_i64, _c_p],
+    "fso_moe_silu_mul_quantize_rows": [_c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p],
     "fso_moe_combine": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
     "fso_gemm_mxfp8_epilogue": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_i64, _c_p, _c_i64,
                                 _c_p],

@@ -221,6 +221,26 @@ def moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn):
                                 int(blk_expert.shape[0]), int(dq.shape[0]), ptr(dn), stream_ptr()), "fso_moe_fc2")
 
 
+def moe_grouped_gemm_decode(act_q, act_sf, weight, sfw, masked_m, blk0, blk_expert, out, tokens: int, topk: int):
+    """out [rows, n_w] (fp32 or bf16, by its dtype) = the routed rows of act_q [rows, K] times weight [E, n_w, K]^T
+    per expert, decode band."""
+    e, n_w, k = (int(v) for v in weight.shape)
+    with torch.cuda.device(act_q.device):
+        check(lib().fso_moe_grouped_gemm_decode(ptr(act_q), ptr(act_sf), ptr(weight), ptr(sfw), ptr(masked_m), ptr(blk0),
+                                                ptr(blk_expert), e, n_w, k, int(blk_expert.shape[0]),
+                                                int(act_q.shape[0]), ptr(out), 1 if out.dtype == torch.float32 else 0,
+                                                int(tokens), int(topk), stream_ptr()),
+              "fso_moe_grouped_gemm_decode")
+
+
+def moe_silu_mul_quantize_rows(gu, masked_m, blk0, blk_expert, num_experts: int, dq, sd):
+    rows, inter = int(dq.shape[0]), int(dq.shape[1])
+    with torch.cuda.device(gu.device):
+        check(lib().fso_moe_silu_mul_quantize_rows(ptr(gu), ptr(masked_m), ptr(blk0), ptr(blk_expert), int(num_experts),
+                                                   rows, inter, ptr(dq), ptr(sd), stream_ptr()),
+              "fso_moe_silu_mul_quantize_rows")
+
+
 def moe_combine(dn, slot, topk_w, bias, bias_scale, out):
     t, h = int(out.shape[0]), int(out.shape[1])
     topk = int(topk_w.shape[1])

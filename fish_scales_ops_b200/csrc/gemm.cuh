@@ -40,6 +40,9 @@ struct GemmParams {
     float* ws;                 // EPI_PARTIAL: fp32 [splits, M, N]
     const int32_t* blk0;       // grouped: blk0[num_experts] = blocks in use
     const int32_t* blk_expert; // grouped: expert of each 128-row block
+    const int32_t* masked_m;   // grouped + swapped: routed rows of each expert
+    int subs;                  // grouped + swapped: token sub-tiles per 128-row block (128 / BN)
+    int out_f32;               // grouped + swapped: `out` is fp32 [rows, ldo] (the accumulators, not rounded)
     int rows_a;                // valid rows of the MMA-M operand
     int rows_b;                // valid rows of the MMA-N operand (per expert when grouped)
     int kb_total;              // K / 128
@@ -117,10 +120,12 @@ struct GemmCfg {
 };
 
 struct TileCoord {
-    int a_tile;     // 128-row tile of the MMA-M operand (grouped: block index)
-    int b_tile;     // BN-row tile of the MMA-N operand
+    int a_tile;     // 128-row tile of the MMA-M operand (grouped: block index; grouped + swapped: weight panel)
+    int b_tile;     // BN-row tile of the MMA-N operand (grouped + swapped: block index)
     int split;
     int expert;     // grouped: expert of the block; otherwise 0
+    int sub;        // grouped + swapped: token sub-tile of the block
+    int live;       // grouped + swapped: routed rows in this sub-tile (<= 0: nothing to do)
 };
 
 // Static schedule: work item t of (tiles_a_used * tiles_b * splits). A tiles advance fastest inside a group of
@@ -142,6 +147,28 @@ __device__ __forceinline__ bool decode_tile(GemmParams const& p, int t, int tile
     c.a_tile = first_a + (in_g - c.b_tile * gsz);
     c.expert = 0;
     if constexpr (kGrouped) c.expert = p.blk_expert[c.a_tile];
+    return true;
+}
+
+// Grouped + swapped (the decode band of the MoE layer): weight rows of one expert on MMA-M, the (few) routed rows of
+// one 128-row block on MMA-N. Work item t of (blocks in use x weight panels x sub-tiles x splits), weight panels
+// fastest so that neighbouring CTAs stream neighbouring weight rows. A sub-tile past the block's routed rows is
+// returned with live <= 0 and skipped by every role.
+template <int BN, bool kClusterK>
+__device__ __forceinline__ bool decode_tile_gs(GemmParams const& p, int t, int blocks_used, TileCoord& c)
+{
+    int const panels = p.tiles_a;
+    int const items = blocks_used * panels * p.subs;
+    if (t >= items * p.splits) return false;
+    c.split = kClusterK ? t % p.splits : t / items;
+    int const r = kClusterK ? t / p.splits : t - c.split * items;
+    c.a_tile = r % panels;
+    int const q = r / panels;
+    c.sub = q % p.subs;
+    c.b_tile = q / p.subs;
+    c.expert = p.blk_expert[c.b_tile];
+    int const in_block = min(128, p.masked_m[c.expert] - 128 * (c.b_tile - p.blk0[c.expert]));
+    c.live = min(BN, in_block - c.sub * BN);
     return true;
 }
 
@@ -235,10 +262,20 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // weight loads while this one runs, and this one has done the same under its predecessor. Before its
     // griddep_wait() a kernel reads only weights (immutable) and writes nothing outside its own CTA.
     if constexpr (kSwap) griddep_launch_dependents();
+    constexpr bool kGS = kSwap && kGrouped;
+    static_assert(!kGS || (BN >= 32 && (EPI == EPI_BF16 || EPI == EPI_CLUSTER)),
+        "grouped + swapped: token tiles of 32 / 64 rows (scale columns cover 32 rows), bf16 output");
+    // the routing tensors are the output of kernels earlier in the stream: nothing of them is read before the wait
+    if constexpr (kGS) griddep_wait();
 
     int tiles_a_used = p.tiles_a;
-    if constexpr (kGrouped) tiles_a_used = min(p.tiles_a, p.blk0[p.num_experts]);
+    if constexpr (kGrouped && !kSwap) tiles_a_used = min(p.tiles_a, p.blk0[p.num_experts]);
+    if constexpr (kGS) tiles_a_used = min(p.tiles_b, p.blk0[p.num_experts]);      // blocks in use
     int const rows_b_pad = (p.rows_b + 127) & ~127;
+    auto next_tile = [&](int t, TileCoord& c) {
+        if constexpr (kGS) return decode_tile_gs<BN, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c);
+        else return decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c);
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
@@ -248,19 +285,24 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             TileCoord c;
             bool ok = true;
             bool first_tile = true;
-            for (int t = blockIdx.x; ok && decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
+            for (int t = blockIdx.x; ok && next_tile(t, c); t += gridDim.x) {
+                if constexpr (kGS) {
+                    if (c.live <= 0) continue;
+                }
                 int kb0 = c.split * p.kb_per_split;
                 int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                int const a_row0 = c.a_tile * C::kBM;
-                int const b_row0 = c.b_tile * BN;
-                int const b_coord = kGrouped ? c.expert * p.rows_b + b_row0 : b_row0;
+                // grouped + swapped: the expert's weight rows follow each other in the [E * rows_a, K] weight, and
+                // the token rows are the block's rows from its sub-tile on
+                int const a_row0 = kGS ? c.expert * p.rows_a + c.a_tile * C::kBM : c.a_tile * C::kBM;
+                int const b_row0 = kGS ? c.b_tile * 128 + c.sub * BN : c.b_tile * BN;
+                int const b_coord = (kGrouped && !kSwap) ? c.expert * p.rows_b + b_row0 : b_row0;
                 const uint8_t* sfb_base = p.sfb
-                    + (kGrouped ? static_cast<int64_t>(c.expert) * (rows_b_pad / 128) * p.kb_total * 512 : 0);
+                    + ((kGrouped && !kSwap) ? static_cast<int64_t>(c.expert) * (rows_b_pad / 128) * p.kb_total * 512 : 0);
                 int sfb_atoms = 0;
                 for (int j = 0; j < C::kSfbAtoms; ++j)
                     if (b_row0 + j * 128 < rows_b_pad) ++sfb_atoms;
                 uint32_t const bytes = C::kABytes + C::kBBytes + C::kSfaBytes + 512u * sfb_atoms;
-                if constexpr (kSwap) {
+                if constexpr (kSwap && !kGrouped) {
                     if (first_tile) {
                         // The weight side (MMA-M operand and its scales) of the first stages goes out before the
                         // wait for the preceding kernel; the activation side, which that kernel may still be
@@ -322,7 +364,10 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t idesc = make_idesc_mxf8(BN);
             TileCoord c;
             bool ok = true;
-            for (int t = blockIdx.x; ok && decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
+            for (int t = blockIdx.x; ok && next_tile(t, c); t += gridDim.x) {
+                if constexpr (kGS) {
+                    if (c.live <= 0) continue;
+                }
                 int const kb0 = c.split * p.kb_per_split;
                 int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 if (!wait_or_abort(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
@@ -331,7 +376,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
                 tc_fence_after();
                 uint32_t const d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                uint32_t const sfb_col_off = BN < 128 ? static_cast<uint32_t>(((c.b_tile * BN) & 127) >> 5) : 0u;
+                uint32_t const sfb_col_off = kGS ? static_cast<uint32_t>((c.sub * BN) >> 5)
+                    : BN < 128 ? static_cast<uint32_t>(((c.b_tile * BN) & 127) >> 5) : 0u;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait_or_abort(full_bar(stage), phase, abort_flag)) {
                         record_abort(FSO_DEV_WAIT_MMA_FULL, abort_flag);
@@ -377,7 +423,10 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         int acc = 0;
         uint32_t acc_phase = 0;
         TileCoord c;
-        for (int t = blockIdx.x; decode_tile<kGrouped, EPI == EPI_CLUSTER>(p, t, tiles_a_used, c); t += gridDim.x) {
+        for (int t = blockIdx.x; next_tile(t, c); t += gridDim.x) {
+            if constexpr (kGS) {
+                if (c.live <= 0) continue;
+            }
             if (!wait_or_abort(tfull_bar(acc), acc_phase, abort_flag)) {
                 if (lane == 0) record_abort(FSO_DEV_WAIT_EPILOGUE, abort_flag);
                 break;
@@ -386,7 +435,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t const t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16)
                 + static_cast<uint32_t>(acc * BN);
             int const a_row = c.a_tile * C::kBM + quarter * 32 + lane;   // this thread's row of the MMA-M operand
-            int const b_row0 = c.b_tile * BN;
+            int const b_row0 = kGS ? c.b_tile * 128 + c.sub * BN : c.b_tile * BN;
+            int const b_bound = kGS ? b_row0 + c.live : p.rows_b;        // swapped: first token row past this tile's
             bool released = false;
 
             if constexpr (EPI == EPI_CLUSTER) {
@@ -634,7 +684,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         int const m = b_row0 + c0 + j;
-                        if (m < p.rows_b && a_row < p.rows_a) {
+                        if (m < b_bound && a_row < p.rows_a) {
                             if constexpr (EPI == EPI_BF16) {
                                 float v = __uint_as_float(r[j]);
                                 if constexpr (kFused) {
@@ -643,8 +693,11 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                     if (p.residual != nullptr)
                                         v += __bfloat162float(p.residual[static_cast<int64_t>(m) * p.ldo + a_row]);
                                 }
-                                static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row]
-                                    = __float2bfloat16_rn(v);
+                                if (kGS && p.out_f32)
+                                    static_cast<float*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row] = v;
+                                else
+                                    static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row]
+                                        = __float2bfloat16_rn(v);
                             } else
                                 p.ws[static_cast<int64_t>(c.split) * p.out_rows * p.ldo
                                     + static_cast<int64_t>(m) * p.ldo + a_row] = __uint_as_float(r[j]);
@@ -686,11 +739,12 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < BN; ++j) red_v[j] += red[((s2 - 1) * BN + j) * 128 + row];
             int const a_row = red_c.a_tile * C::kBM + row;
-            int const b_row0 = red_c.b_tile * BN;
+            int const b_row0 = kGS ? red_c.b_tile * 128 + red_c.sub * BN : red_c.b_tile * BN;
+            int const b_bound = kGS ? b_row0 + red_c.live : p.rows_b;
 #pragma unroll
             for (int j = 0; j < BN; ++j) {
                 int const m = b_row0 + j;
-                if (m < p.rows_b && a_row < p.rows_a) {
+                if (m < b_bound && a_row < p.rows_a) {
                     float v = red_v[j];
                     if constexpr (kFused) {
                         v = epilogue_value(v, p.bias != nullptr ? bias_term(p.bias[a_row]) : 0.f, p.bias != nullptr,
@@ -698,7 +752,10 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         if (p.residual != nullptr)
                             v += __bfloat162float(p.residual[static_cast<int64_t>(m) * p.ldo + a_row]);
                     }
-                    static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row] = __float2bfloat16_rn(v);
+                    if (kGS && p.out_f32)
+                        static_cast<float*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row] = v;
+                    else
+                        static_cast<__nv_bfloat16*>(p.out)[static_cast<int64_t>(m) * p.ldo + a_row] = __float2bfloat16_rn(v);
                 }
             }
         }

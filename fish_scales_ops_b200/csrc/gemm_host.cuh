@@ -261,11 +261,16 @@ inline int cluster_capacity_bn(int bn, int splits, bool fused)
 }
 
 // The swapped kernel with split-K inside thread-block clusters of `splits` CTAs (one CTA per work item).
-template <int BN, bool kFused = false>
+template <int BN, bool kFused = false, bool kGrouped = false>
 inline int launch_gemm_cluster(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int items,
     cudaStream_t stream)
 {
-    auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, false, kFused>;
+    auto kernel = gemm_mxf8_kernel<BN, EPI_CLUSTER, true, kGrouped, kFused>;
+    if constexpr (kGrouped) {
+        static std::atomic<uint64_t> done{0};
+        int const rc = ensure_smem_attr(kernel, GemmCfg<BN, EPI_CLUSTER>::kSmemBytes, done);
+        if (rc != 0) return rc;
+    }
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     cluster_launch_config<BN>(cfg, attr, items, p.splits, stream);
@@ -579,4 +584,62 @@ inline int launch_grouped(const void* a, const void* sfa, const void* weight, co
     return launch_gemm_inst<128, EPI_BF16, false, true>(ta, tb, p, grid, stream);
 }
 
+// The grouped GEMM of the MoE layer's decode band (at most 64 tokens): weight rows on MMA-M, the routed rows of one
+// 128-row block of the compact activation on MMA-N in tiles of 32 / 64, one tile per (block in use, 128 weight rows,
+// sub-tile); out = [rows, n_w], fp32 for FC1 (the interleaved gate / up accumulators, which the activation kernel
+// behind it reads unrounded) and bf16 for FC2 (the down projection). With few
+// experts in use and a long K the K blocks of a tile are split over the CTAs of a cluster (one launch, summed in
+// slice order through distributed shared memory), otherwise persistent half-SM CTAs walk the tiles.
+// `pairs` = tokens * top-k of the call: with the shapes it fixes every host decision (capturable, no device read).
+inline int launch_grouped_swap(const void* a, const void* sfa, const void* weight, const void* sfw,
+    const int32_t* masked_m, const int32_t* blk0, const int32_t* blk_expert, int64_t num_experts, int64_t n_w, int64_t k,
+    int64_t num_blocks, int64_t rows, void* out, bool out_f32, int64_t tokens, int64_t pairs, cudaStream_t stream)
+{
+    int const sms = sm_count();
+    int const bn = tokens <= 32 ? 32 : 64;
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_operand_map(&ta, weight, num_experts * n_w, k, 128)) != 0) return rc;
+    if ((rc = make_operand_map(&tb, a, rows, k, bn)) != 0) return rc;
+    GemmParams p{};
+    p.sfa = static_cast<const uint8_t*>(sfw);
+    p.sfb = static_cast<const uint8_t*>(sfa);
+    p.out = out;
+    p.blk0 = blk0;
+    p.blk_expert = blk_expert;
+    p.masked_m = masked_m;
+    p.rows_a = static_cast<int>(n_w);
+    p.rows_b = static_cast<int>(rows);
+    p.kb_total = static_cast<int>(k / 128);
+    p.tiles_a = static_cast<int>(n_w / 128);
+    p.tiles_b = static_cast<int>(num_blocks);
+    p.subs = 128 / bn;
+    p.ldo = static_cast<int>(n_w);
+    p.num_experts = static_cast<int>(num_experts);
+    p.group_a = 1;
+    p.out_rows = rows;
+    p.out_f32 = out_f32 ? 1 : 0;
+    // expected live tiles: one block per expert in use (an expert holds at most `tokens` <= 64 rows when a token
+    // names an expert once), every weight panel of it
+    int64_t const live_experts = pairs < num_experts ? pairs : num_experts;
+    int64_t const live_tiles = live_experts * p.tiles_a;
+    int splits = 1, kb_per = p.kb_total;
+    pick_decode_splits(live_tiles, p.kb_total, cluster_split_limit(bn), &splits, &kb_per);
+    p.splits = splits;
+    p.kb_per_split = kb_per;
+    int64_t const bound = num_blocks * p.tiles_a * p.subs * splits;      // every tile a routing could make live
+    if (bound >= (1ll << 30)) {
+        set_error("fso_moe_grouped_gemm_decode: the tile space is beyond the kernel's index range");
+        return FSO_ERR_INVALID;
+    }
+    if (splits > 1) {
+        return bn == 32 ? launch_gemm_cluster<32, false, true>(ta, tb, p, static_cast<int>(bound), stream)
+                        : launch_gemm_cluster<64, false, true>(ta, tb, p, static_cast<int>(bound), stream);
+    }
+    int const grid = static_cast<int>(bound < 2 * sms ? bound : 2 * sms);
+    return bn == 32 ? launch_gemm_inst<32, EPI_BF16, true, true>(ta, tb, p, grid, stream)
+                    : launch_gemm_inst<64, EPI_BF16, true, true>(ta, tb, p, grid, stream);
+}
+
 }  // namespace fso
+

@@ -452,6 +452,38 @@ int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2,
         as_stream(stream));
 }
 
+int fso_moe_grouped_gemm_decode(const void* act_q, const void* act_sf, const void* weight, const void* sfw,
+    const int32_t* masked_m, const int32_t* blk0, const int32_t* blk_expert, int64_t num_experts, int64_t n_w, int64_t k,
+    int64_t num_blocks, int64_t rows, void* out, int64_t out_is_f32, int64_t tokens, int64_t topk, void* stream)
+{
+    FSO_REQUIRE(num_experts >= 1 && num_experts <= 1024 && n_w > 0 && k > 0 && n_w % 128 == 0 && k % 128 == 0,
+        "fso_moe_grouped_gemm_decode: 1 <= E <= 1024 and N_w, K multiples of 128 required");
+    FSO_REQUIRE(num_blocks >= 1 && rows >= 128 * num_blocks && rows % 128 == 0,
+        "fso_moe_grouped_gemm_decode: rows = %lld must be a multiple of 128 covering num_blocks = %lld blocks",
+        static_cast<long long>(rows), static_cast<long long>(num_blocks));
+    FSO_REQUIRE(tokens >= 1 && tokens <= 64 && topk >= 1,
+        "fso_moe_grouped_gemm_decode: serves 1 to 64 tokens, got %lld (larger batches take fso_moe_fc1_swiglu / "
+        "fso_moe_fc2)", static_cast<long long>(tokens));
+    FSO_REQUIRE(num_experts * n_w < (1ll << 31) && rows < (1ll << 31), "fso_moe_grouped_gemm_decode: dimension too large");
+    FSO_REQUIRE(act_q && act_sf && weight && sfw && masked_m && blk0 && blk_expert && out,
+        "fso_moe_grouped_gemm_decode: NULL pointer");
+    FSO_REQUIRE(aligned16(act_q) && aligned16(act_sf) && aligned16(weight) && aligned16(sfw) && aligned16(out),
+        "fso_moe_grouped_gemm_decode: every operand must be 16-byte aligned");
+    return launch_grouped_swap(act_q, act_sf, weight, sfw, masked_m, blk0, blk_expert, num_experts, n_w, k, num_blocks,
+        rows, out, out_is_f32 != 0, tokens, tokens * topk, as_stream(stream));
+}
+
+int fso_moe_silu_mul_quantize_rows(const void* gu, const int32_t* masked_m, const int32_t* blk0,
+    const int32_t* blk_expert, int64_t num_experts, int64_t rows, int64_t inter, void* dq, void* sd, void* stream)
+{
+    FSO_REQUIRE(num_experts >= 1 && rows > 0 && rows % 128 == 0 && inter > 0 && inter % 128 == 0,
+        "fso_moe_silu_mul_quantize_rows: rows and I must be positive multiples of 128");
+    FSO_REQUIRE(gu && masked_m && blk0 && blk_expert && dq && sd, "fso_moe_silu_mul_quantize_rows: NULL pointer");
+    FSO_REQUIRE((reinterpret_cast<uintptr_t>(gu) & 31u) == 0 && aligned16(dq) && (reinterpret_cast<uintptr_t>(sd) & 3u) == 0,
+        "fso_moe_silu_mul_quantize_rows: gu must be 32-byte aligned, dq 16-byte aligned and sd 4-byte aligned");
+    return launch_silu_mul_quantize_rows(gu, dq, sd, masked_m, blk0, blk_expert, num_experts, rows, inter, as_stream(stream));
+}
+
 // A multiplier coprime to n (a prime that does not divide it): v -> (v * mul) mod n is then a permutation of [0, n).
 static int64_t coprime_multiplier(int64_t n)
 {

@@ -365,6 +365,92 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const uint8_t* _
     if (sub == 0) sf[sf_word_index(row, kp, kb)] = live ? word : 0u;
 }
 
+// The same step for the decode band of the MoE layer: gu is the fp32 [rows, 2I] output of the grouped FC1 over the
+// compact activation (the accumulators, so that the activation sees what the fused epilogue of the prefill kernels
+// sees) with its columns in the experts' interleaved order (gate_j, up_j adjacent); only the routed rows of the
+// blocks in use are read and written (row r of block b is routed when r % 128 < rows of the block's expert that fall
+// into this block). 16 outputs per thread from 128 contiguous input bytes.
+__global__ void __launch_bounds__(256) silu_mul_quantize_rows_kernel(const uint8_t* __restrict__ gu,
+    uint4* __restrict__ q, uint32_t* __restrict__ sf, const int32_t* __restrict__ masked_m,
+    const int32_t* __restrict__ blk0, const int32_t* __restrict__ blk_expert, int num_experts, uint32_t rows_bound,
+    uint32_t kb)
+{
+    griddep_launch_dependents();
+    griddep_wait();
+    uint32_t const sub = threadIdx.x & 7;
+    uint32_t const c = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    if (c >= rows_bound * kb) return;                                       // whole groups of 8 lanes leave together
+    uint32_t const row = c / kb;
+    uint32_t const kp = c - row * kb;
+    int const block = static_cast<int>(row >> 7);
+    bool live = false;
+    if (block < __ldg(blk0 + num_experts)) {
+        int const e = __ldg(blk_expert + block);
+        live = static_cast<int>(row & 127u) < __ldg(masked_m + e) - 128 * (block - __ldg(blk0 + e));
+    }
+    uint32_t v[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j][i] = 0;
+    if (live) {
+        const uint8_t* const src = gu + (static_cast<size_t>(row) * kb + kp) * 1024 + sub * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ld_nc_256(src + 32 * j, v[j]);
+    }
+    float h[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float const g0 = __uint_as_float(v[i >> 2][2 * (i & 3)]), u0 = __uint_as_float(v[i >> 2][2 * (i & 3) + 1]);
+        float t0;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(0.5f * g0));
+        h[i] = (0.5f * g0) * (1.f + t0) * u0;
+        amax = fmaxf(amax, fabsf(h[i]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, 1e-10f);
+    float qs;
+    uint32_t const byte = e8m0_from_amax(amax, qs);
+    uint32_t const word = word_from_8lanes(byte, sub);
+    if (live) {
+        uint4 o;
+        o.x = fp8x4(__fmul_rn(h[0], qs), __fmul_rn(h[1], qs), __fmul_rn(h[2], qs), __fmul_rn(h[3], qs));
+        o.y = fp8x4(__fmul_rn(h[4], qs), __fmul_rn(h[5], qs), __fmul_rn(h[6], qs), __fmul_rn(h[7], qs));
+        o.z = fp8x4(__fmul_rn(h[8], qs), __fmul_rn(h[9], qs), __fmul_rn(h[10], qs), __fmul_rn(h[11], qs));
+        o.w = fp8x4(__fmul_rn(h[12], qs), __fmul_rn(h[13], qs), __fmul_rn(h[14], qs), __fmul_rn(h[15], qs));
+        q[(static_cast<size_t>(row) * kb + kp) * 8 + sub] = o;
+        if (sub == 0) sf[sf_word_index(row, kp, kb)] = word;
+    }
+}
+
+inline int launch_silu_mul_quantize_rows(const void* gu, void* q, void* sf, const int32_t* masked_m, const int32_t* blk0,
+    const int32_t* blk_expert, int64_t num_experts, int64_t rows_bound, int64_t inter, cudaStream_t stream)
+{
+    int const kb = static_cast<int>(inter / 128);
+    if (rows_bound * kb >= (1ll << 28)) {
+        set_error("fso_moe_silu_mul_quantize_rows: %lld x %lld is beyond the kernel's index range",
+            static_cast<long long>(rows_bound), static_cast<long long>(inter));
+        return FSO_ERR_INVALID;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>((rows_bound * kb * 8 + 255) / 256), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (quantizer_pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
+    FSO_CUDA(cudaLaunchKernelEx(&cfg, silu_mul_quantize_rows_kernel, static_cast<const uint8_t*>(gu),
+        static_cast<uint4*>(q), static_cast<uint32_t*>(sf), masked_m, blk0, blk_expert, static_cast<int>(num_experts),
+        static_cast<uint32_t>(rows_bound), static_cast<uint32_t>(kb)));
+    return launch_status("silu_mul_quantize_rows_kernel");
+}
+
 inline int launch_silu_mul_quantize(const void* gu, void* q, void* sf, int64_t m, int64_t inter, cudaStream_t stream)
 {
     int64_t const m_pad = (m + 127) / 128 * 128;

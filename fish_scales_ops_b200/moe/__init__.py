@@ -24,6 +24,38 @@ _UNSERVED = ("bf16", "bfloat16", "fp16", "float16", "fp32", "float32", "fp8", "i
              "int4", "w4a16", "w4a8", "mxfp4", "nvfp4")
 FP8 = torch.float8_e4m3fn
 _REGION_ALIGN = 1024
+# The decode band (the reference's slot route, python/fish_scales_ops/gemm/mxfp8.py:540-551: "expected rows per expert
+# <= 64"): calls of at most 64 tokens whose routed pairs are at most twice the experts they can reach, so that an
+# expert in use holds a row or two. There the swapped grouped GEMM (weights on MMA-M, only the experts in use) beats
+# the 128-row tiles of the prefill kernels: measured under CUDA-graph replay, Mixtral 1 token 111 -> 84 us, 4 tokens
+# 136 -> 121 us, DeepSeek-V3 16 tokens 841 -> 772 us, 64 tokens 1674 -> 1575 us (0.98 of the live weights' stream);
+# with more rows per expert (Mixtral 16 / 64 tokens) the prefill kernels stream the weights faster and keep the call.
+# FC2 takes the band whenever the call is in it; FC1 only when its live tiles fill the half-SM CTA slots one and a
+# half times over (otherwise the fused prefill FC1, with its 256-row weight tiles, is ahead: DeepSeek-V3 1 token).
+# Both choices are functions of (tokens, top-k, E, I, SM count) alone, so a captured graph replays for any routing.
+# FSO_B200_MOE_DECODE=0 sends every call through the prefill kernels, =force every call of at most 64 tokens through
+# the band (tests).
+_DECODE_TOKENS = 64
+
+
+def _sm_count() -> int:
+    return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+
+
+def _decode_band(tokens: int, topk: int, num_experts: int, inter: int):
+    """(FC1 takes the decode band, FC2 takes the decode band)."""
+    import os
+
+    mode = os.environ.get("FSO_B200_MOE_DECODE", "1")
+    if not 0 < tokens <= _DECODE_TOKENS or mode == "0":
+        return False, False
+    if mode == "force":
+        return True, True
+    pairs = tokens * topk
+    live = min(pairs, num_experts)
+    if pairs > 2 * live:
+        return False, False
+    return live * (2 * inter // 128) >= 3 * _sm_count(), True
 
 
 def supported(format, arch=None) -> bool:
@@ -50,7 +82,9 @@ def describe() -> str:
         "float8_e4m3fn experts with uint8 UE8M0 scales keep their bytes and get their scales packed.",
         "format 'bsfp8': float8_e4m3fn experts with fp32 128x128 block scales are requantized to MXFP8 1x32.",
         "layer(): compact routing (deterministic order), token gather + quantize, grouped tcgen05 GEMM with the "
-        "fused SiLU(gate)*up requantize, grouped GEMM, top-k weighted un-permute. Top-k ids outside [0, E_local) are "
+        "fused SiLU(gate)*up requantize, grouped GEMM, top-k weighted un-permute; calls of at most 64 tokens with a "
+        "row or two per expert take the decode band instead (weights of the experts in use on MMA-M, SiLU(gate)*up as "
+        "a row-wise kernel between the two GEMMs). Top-k ids outside [0, E_local) are "
         "skipped at no expert cost, and the result is this rank's partial sum, which the caller reduces across ranks.",
     ]
     if arch // 10 != SERVED_MAJOR:
@@ -230,6 +264,8 @@ class _LayerPlan:
     route_scratch: int
     sh_off: int
     region: int
+    gate_up: int       # bytes of the fp32 [rows, 2I] FC1 output of the decode band (0 when FC1 stays fused)
+    fc2_decode: bool   # FC2 takes the decode band
 
 
 def _layer_plan(tokens: int, topk: int, num_experts: int, hidden: int, inter: int) -> _LayerPlan:
@@ -237,8 +273,9 @@ def _layer_plan(tokens: int, topk: int, num_experts: int, hidden: int, inter: in
     rows = int(p.rows)
     sh_off = _align_up(rows * hidden, _REGION_ALIGN)
     front = sh_off + 4 * rows * (hidden // 128)
+    fc1_decode, fc2_decode = _decode_band(tokens, topk, num_experts, inter)
     return _LayerPlan(int(p.pairs), int(p.num_blocks), rows, int(p.route_scratch_bytes), sh_off,
-                      max(front, 2 * rows * hidden))
+                      max(front, 2 * rows * hidden), 8 * rows * inter if fc1_decode else 0, fc2_decode)
 
 
 def _plan_bytes(plan: _LayerPlan, tokens: int, num_experts: int, hidden: int, inter: int) -> int:
@@ -247,6 +284,7 @@ def _plan_bytes(plan: _LayerPlan, tokens: int, num_experts: int, hidden: int, in
     total += a(plan.route_scratch)
     total += a(plan.region)
     total += a(plan.rows * inter) + a(4 * plan.rows * (inter // 128))
+    total += a(plan.gate_up)
     total += a(2 * tokens * hidden)
     return total
 
@@ -284,9 +322,19 @@ def _run_layer(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale):
         sd = torch.empty((plan.rows * (inter // 128),), dtype=torch.int32, device=dev)
         out = torch.empty((t, h), dtype=torch.bfloat16, device=dev)
         _ops.moe_gather_quant(hidden, slot, topk, hq, sh)
-        _ops.moe_fc1_swiglu(hq, sh, w13, sw13, blk0, blk_expert, dq, sd)
+        if plan.gate_up > 0:
+            # decode band: only the experts in use are touched, their weights on MMA-M; FC1's fp32 gate / up
+            # accumulators go through the row-wise silu(gate) * up requantizer
+            gu = torch.empty((plan.rows, 2 * inter), dtype=torch.float32, device=dev)
+            _ops.moe_grouped_gemm_decode(hq, sh, w13, sw13, masked_m, blk0, blk_expert, gu, t, topk)
+            _ops.moe_silu_mul_quantize_rows(gu, masked_m, blk0, blk_expert, e, dq, sd)
+        else:
+            _ops.moe_fc1_swiglu(hq, sh, w13, sw13, blk0, blk_expert, dq, sd)
         dn = region[:2 * plan.rows * h].view(torch.bfloat16).view(plan.rows, h)
-        _ops.moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn)
+        if plan.fc2_decode:
+            _ops.moe_grouped_gemm_decode(dq, sd, w2, sw2, masked_m, blk0, blk_expert, dn, t, topk)
+        else:
+            _ops.moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn)
         _ops.moe_combine(dn, slot, topk_w, bias, bias_scale, out)
     return out
 

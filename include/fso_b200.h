@@ -174,6 +174,27 @@ int fso_moe_fc2(const void* dq, const void* sd, const void* w2, const void* sw2,
                 const int32_t* blk_expert, int64_t num_experts, int64_t h, int64_t inter, int64_t num_blocks,
                 int64_t rows, void* dn, void* stream);
 
+/* The grouped GEMMs of the layer's decode band (1 to 64 tokens), in the swapped orientation: the weight rows of the
+ * experts in use on MMA-M, each expert's few routed rows on MMA-N in tiles of 32 / 64, one tile per (block in use,
+ * 128 weight rows); nothing is computed for experts no token chose, and every weight byte is streamed once.
+ * out = [rows, n_w], fp32 when out_is_f32 != 0 and bf16 otherwise: for FC1 (weight w13 [E, 2I, H], n_w = 2I, k = H)
+ * the fp32 gate / up accumulators in the experts' interleaved column order, for FC2 (weight w2 [E, H, I], n_w = H,
+ * k = I) the bf16 down projection. Few live tiles and a long K:
+ * K is split inside thread-block clusters (one launch, ordered sum). Every host decision is a function of the shapes,
+ * tokens and topk. Between the two calls fso_moe_silu_mul_quantize_rows turns FC1's fp32 output gu into FC2's
+ * activation: silu(gate) * up with the 1x32 rule, routed rows only.
+ * Replaces the compact slot route: ops linear_mxfp8_grouped_compact[_swiglu] below the band rule of
+ * python/fish_scales_ops/gemm/mxfp8.py:540-551, kernels csrc/gemm/include/blockscale_gemm/arch/sm100/mxfp8/
+ * grouped_slot_dispatch.cuh:1-110, and the unfused FC1 arm silu_chunk_mul_quantize_1x32_grouped_out
+ * (csrc/gemm/ops/mxfp8_compact.cu:258, quant_kernels.cu:2131-2251). The reference's single persistent FC1 + FC2
+ * kernel (csrc/gemm/ops/mxfp8.cu:1546, slot_moe_scheduler.cuh) is three launches here, chained with programmatic
+ * dependent launch. */
+int fso_moe_grouped_gemm_decode(const void* act_q, const void* act_sf, const void* weight, const void* sfw,
+    const int32_t* masked_m, const int32_t* blk0, const int32_t* blk_expert, int64_t num_experts, int64_t n_w, int64_t k,
+    int64_t num_blocks, int64_t rows, void* out, int64_t out_is_f32, int64_t tokens, int64_t topk, void* stream);
+int fso_moe_silu_mul_quantize_rows(const void* gu, const int32_t* masked_m, const int32_t* blk0,
+    const int32_t* blk_expert, int64_t num_experts, int64_t rows, int64_t inter, void* dq, void* sd, void* stream);
+
 /* out[t] = bf16( sum_j w[t,j] * dn[slot_of_flat[t*topk+j]] (+ bias_scale[t] * bias[t]) ), fp32, j ascending.
  * bias / bias_scale may be NULL. Replaces: moe_combine, csrc/gemm/ops/moe_glue.cu:2908-3016. */
 int fso_moe_combine(const void* dn, const int32_t* slot_of_flat, const float* topk_w, const void* bias,

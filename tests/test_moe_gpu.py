@@ -249,3 +249,79 @@ def test_layer_graph_replay_with_rewritten_routing(fso, device_ok):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, fso.moe.layer(hidden, ex, ids, wts))
+
+
+# ------------------------------------------------------------------------------------------------ the decode band
+
+# (tokens, experts, topk, H, I, draw): at most 64 tokens -> the swapped grouped GEMMs. "dup" names one expert twice in
+# a token, so an expert holds more rows than there are tokens (a second token sub-tile of its block, and with 64
+# tokens a second 128-row block of the expert); "hot" fills one expert's block to the token count.
+DECODE_CASES = [(1, 8, 2, 512, 256, "random"), (7, 8, 2, 256, 384, "random"), (16, 16, 4, 512, 256, "skew"),
+                (33, 8, 2, 256, 256, "hot"), (64, 8, 2, 512, 512, "random"), (64, 16, 4, 256, 128, "hot"),
+                (40, 8, 2, 256, 256, "dup"), (64, 8, 4, 256, 128, "dup"), (48, 8, 2, 256, 256, "ep"),
+                (64, 256, 8, 256, 128, "random"), (2, 8, 2, 1024, 3584, "random")]
+
+
+@pytest.mark.parametrize("t,e,k,h,i,kind", DECODE_CASES)
+def test_decode_band_matches_oracle_and_prefill_route(fso, oracle, device_ok, t, e, k, h, i, kind, monkeypatch):
+    w13, w2, ex = _prepare(fso, e, h, i, 150 + t)
+    ids = _draw(t, e, k, "random" if kind == "dup" else kind, 160 + t)
+    if kind == "dup":
+        ids[:, 1] = ids[:, 0]                  # the same expert twice: 2 rows of that expert per token
+        if k > 2:
+            ids[:, 3] = ids[:, 0]
+    wts = inputs.routing(t, e, k, 160 + t)[1]
+    hidden = inputs.activation(t, h, 170 + t)
+    monkeypatch.setenv("FSO_B200_MOE_DECODE", "force")
+    out = fso.moe.layer(hidden.cuda(), ex, ids.cuda(), wts.cuda())
+    ref = oracle.moe_layer(hidden, inputs.to_np_u8(ex.w13), inputs.to_np_u32(ex.sw13), inputs.to_np_u8(ex.w2),
+                           inputs.to_np_u32(ex.sw2), ids, wts, interleaved=True)
+    inputs.assert_close_to_oracle(out, ref, f"decode band T={t} E={e} k={k} {kind}")
+    # the prefill kernels on the same call: same result up to the output tolerance
+    monkeypatch.setenv("FSO_B200_MOE_DECODE", "0")
+    pre = fso.moe.layer(hidden.cuda(), ex, ids.cuda(), wts.cuda())
+    inputs.assert_close_to_oracle(pre, ref, f"prefill route T={t}")
+    assert inputs.rel_frobenius(out.float().cpu(), pre.float().cpu()) <= 1e-2
+    # the route the layer picks by itself (either GEMM may take the band) agrees as well
+    monkeypatch.delenv("FSO_B200_MOE_DECODE")
+    auto = fso.moe.layer(hidden.cuda(), ex, ids.cuda(), wts.cuda())
+    inputs.assert_close_to_oracle(auto, ref, f"default route T={t}")
+    # bias and bias_scale ride the same combine
+    monkeypatch.setenv("FSO_B200_MOE_DECODE", "force")
+    bias = inputs.activation(t, h, 180 + t)
+    bs = torch.rand(t, generator=inputs.gen(181))
+    with_b = fso.moe.layer(hidden.cuda(), ex, ids.cuda(), wts.cuda(), bias=bias.cuda(), bias_scale=bs.cuda())
+    ref_b = ref + bs[:, None] * bias.float()
+    inputs.assert_close_to_oracle(with_b, ref_b, f"decode band with bias T={t}")
+    # run to run identical
+    again = fso.moe.layer(hidden.cuda(), ex, ids.cuda(), wts.cuda())
+    assert torch.equal(again, out)
+
+
+def test_decode_band_graph_replay_with_rewritten_routing(fso, device_ok, monkeypatch):
+    monkeypatch.setenv("FSO_B200_MOE_DECODE", "force")
+    e, h, i, k, t = 16, 512, 256, 4, 24
+    _, _, ex = _prepare(fso, e, h, i, 27)
+    hidden = inputs.activation(t, h, 28).cuda()
+    ids, wts = inputs.routing(t, e, k, 29)
+    ids, wts = ids.cuda(), wts.cuda()
+    eager = fso.moe.layer(hidden, ex, ids, wts)
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        fso.moe.layer(hidden, ex, ids, wts)
+        with torch.cuda.graph(graph, stream=stream):
+            out = fso.moe.layer(hidden, ex, ids, wts)
+    torch.cuda.current_stream().wait_stream(stream)
+    out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    for seed, skew in ((30, 1.2), (31, 0.0)):
+        ids2, wts2 = inputs.routing(t, e, k, seed, skew=skew)
+        ids.copy_(ids2.cuda())
+        wts.copy_(wts2.cuda())
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, fso.moe.layer(hidden, ex, ids, wts))
