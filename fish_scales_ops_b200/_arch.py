@@ -1,5 +1,7 @@
 """Architecture probe shared by the dense and MoE modules (python/fish_scales_ops/_arch.py and
 python/fish_scales_ops/moe/__init__.py:79-97 of the reference): device 0 decides, resolved once."""
+import re
+
 import torch
 
 _arch_cache = -1
@@ -25,35 +27,36 @@ def arch_label(arch: int) -> str:
     return f"sm_{arch}" if arch > 0 else "no CUDA device"
 
 
+_ARCH_TEXT = re.compile(r"^(?:sm_?)?(\d+)(?:\.(\d+))?[af]?$")
+
+
+def _major_of_number(n: int):
+    """9, 10, 12 are majors as they stand; 90, 100, 103, 120, 121 carry the minor in the last digit."""
+    if 0 < n < 20:
+        return n
+    if 20 <= n < 1000:
+        return n // 10
+    return None
+
+
 def arch_major(arch) -> int:
-    """The compute-capability major of an ``arch`` argument: an int major (9, 10, 12), an int
-    ``major * 10 + minor`` (90, 100, 103, 120, 121), a ``(major, minor)`` pair, or a string such as ``"sm_90"``,
-    ``"sm_100a"``, ``"120"`` or ``"12.0"`` (the forms python/fish_scales_ops/moe/__init__.py:129-156 of the
-    reference takes). Anything that names no compute capability raises ValueError."""
-    if isinstance(arch, bool):
-        raise ValueError(f"arch must name a compute capability, got {arch!r}")
-    if isinstance(arch, (tuple, list)) and len(arch) == 2 and all(isinstance(v, int) for v in arch):
-        return int(arch[0])
+    """Compute-capability major named by ``arch``. Accepted spellings, after the ``arch`` argument of
+    python/fish_scales_ops/moe/__init__.py:129-156 of the reference: a major (10), ``major * 10 + minor`` (100, 103),
+    a ``(major, minor)`` pair, and the text forms ``"sm_100"``, ``"sm100a"``, ``"100"``, ``"10.0"``. ValueError for
+    anything else (booleans included)."""
+    major = None
     if isinstance(arch, str):
-        s = arch.strip().lower()
-        if s.startswith("sm_"):
-            s = s[3:]
-        elif s.startswith("sm"):
-            s = s[2:]
-        if "." in s:
-            head = s.split(".", 1)[0]
-            if head.isdigit():
-                return int(head)
-        s = s.rstrip("af")
-        if not s.isdigit():
-            raise ValueError(f"arch {arch!r} does not name a compute capability (e.g. 'sm_90', 'sm_120')")
-        arch = int(s)
-    if isinstance(arch, int):
-        if 0 < arch < 20:
-            return arch
-        if 20 <= arch < 1000:
-            return arch // 10
-    raise ValueError(f"arch {arch!r} does not name a compute capability (e.g. 'sm_90', 'sm_120')")
+        m = _ARCH_TEXT.match(arch.strip().lower())
+        if m is not None:
+            major = int(m.group(1)) if m.group(2) is not None else _major_of_number(int(m.group(1)))
+    elif isinstance(arch, (tuple, list)):
+        if len(arch) == 2 and all(isinstance(v, int) and not isinstance(v, bool) for v in arch):
+            major = int(arch[0])
+    elif isinstance(arch, int) and not isinstance(arch, bool):
+        major = _major_of_number(arch)
+    if major is None:
+        raise ValueError(f"arch = {arch!r} is not a compute capability; write it like 'sm_100', 100, 10 or (10, 0)")
+    return major
 
 
 def env_flag(name: str, default: bool = False) -> bool:

@@ -90,11 +90,10 @@ class DenseWeight:
 
 
 def _aligned_storage(t: torch.Tensor, align: int = 16) -> torch.Tensor:
-    if t.numel() == 0 or t.data_ptr() % align == 0:
-        return t
-    out = torch.empty_strided(tuple(t.shape), tuple(t.stride()), dtype=t.dtype, device=t.device)
-    out.copy_(t)
-    return out
+    """``t`` itself when its first byte sits on an ``align``-byte boundary, else a copy with the same strides (the
+    allocator's blocks start on 512-byte boundaries). TMA reads the handle's tensors in place."""
+    misaligned = t.numel() > 0 and t.data_ptr() % align != 0
+    return torch.empty_strided(t.size(), t.stride(), dtype=t.dtype, device=t.device).copy_(t) if misaligned else t
 
 
 def _format_error(format, where: str) -> Exception:
@@ -285,20 +284,22 @@ def _check_epilogue(ctx: str, m: int, n: int, device, bias, residual, activation
 
 
 def _check_operands(op: str, x, weight, x_scale) -> None:
-    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
-        raise ValueError(f"{op}: x must be [M, K] and weight [N, K] with the same K, got {tuple(x.shape)} and "
+    """Shapes and dtypes of the op's three main tensors (metadata only)."""
+    shapes_fit = x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1]
+    if not shapes_fit:
+        raise ValueError(f"{op}: expected x [M, K] and weight [N, K] sharing K; x is {tuple(x.shape)}, weight is "
                          f"{tuple(weight.shape)}")
     if weight.dtype != FP8:
-        raise ValueError(f"{op}: weight must be float8_e4m3fn, got {weight.dtype}")
-    if x_scale is None:
-        if x.dtype == FP8:
-            raise ValueError(f"{op}: x is float8_e4m3fn but no x_scale was given; a pre-quantized activation comes "
-                             f"with its scale (fso.dense.quantize_activation)")
-        if x.dtype != torch.bfloat16:
-            raise ValueError(f"{op}: x must be bf16, got {x.dtype}")
-    elif x.dtype == torch.bfloat16:
-        raise ValueError(f"{op}: x_scale was given with a bf16 x; x_scale belongs to the float8_e4m3fn x of "
-                         f"fso.dense.quantize_activation")
+        raise ValueError(f"{op}: the weight is {weight.dtype}; a prepared weight is float8_e4m3fn")
+    quantized_x = x.dtype == FP8
+    if x_scale is None and quantized_x:
+        raise ValueError(f"{op}: a float8_e4m3fn x is a pre-quantized activation and needs the x_scale that "
+                         f"fso.dense.quantize_activation returned with it")
+    if x_scale is None and x.dtype != torch.bfloat16:
+        raise ValueError(f"{op}: x is {x.dtype}; the op takes bf16 (or float8_e4m3fn together with x_scale)")
+    if x_scale is not None and x.dtype == torch.bfloat16:
+        raise ValueError(f"{op}: x_scale goes with the float8_e4m3fn activation of fso.dense.quantize_activation, "
+                         f"but x is bf16")
 
 
 def _check_weight_scale(op: str, kind: str, scale, n: int, k: int) -> None:
@@ -324,34 +325,41 @@ def _check_weight_aligned(op: str, weight, scale) -> None:
 
 
 def _check_xq(op: str, x, device) -> None:
+    """The pre-quantized activation: e4m3, on the weight's device, dense rows, first byte on a 16-byte boundary."""
+    problems = []
     if x.dtype != FP8:
-        raise ValueError(f"{op}: with x_scale, x must be the float8_e4m3fn [M, K] activation of "
-                         f"fso.dense.quantize_activation, got {x.dtype}")
+        problems.append(f"its dtype is {x.dtype}, not float8_e4m3fn")
     if x.device != device:
-        raise ValueError(f"{op}: x is on {x.device} and the weight on {device}")
+        problems.append(f"it lives on {x.device} while the weight lives on {device}")
     if not x.is_contiguous():
-        raise ValueError(f"{op}: the float8_e4m3fn activation must be contiguous, got strides {tuple(x.stride())}")
-    if x.numel() > 0 and x.data_ptr() % 16 != 0:
-        raise ValueError(f"{op}: the float8_e4m3fn activation's data pointer is not 16-byte aligned")
+        problems.append(f"it is not contiguous (strides {tuple(x.stride())})")
+    elif x.numel() > 0 and x.data_ptr() % 16 != 0:
+        problems.append("its data pointer is not a multiple of 16 bytes")
+    if problems:
+        raise ValueError(f"{op}: x passed with x_scale must be the [M, K] activation fso.dense.quantize_activation "
+                         f"returned; " + "; ".join(problems))
 
 
 def _check_x_scale(op: str, x_scale, m: int, k: int, device) -> None:
+    """The scale tensor of a pre-quantized [m, k] activation, against activation contract v1."""
     words = _act_scale_words(m, k)
-    head = (f"{op}: x_scale does not follow activation contract v1 of this device (expected int32 [{words}], the "
-            f"1-D atom layout of an [M, K] = [{m}, {k}] activation)")
     if not isinstance(x_scale, torch.Tensor):
-        raise ValueError(f"{head}; got {type(x_scale).__name__}")
-    if x_scale.dtype != torch.int32:
-        raise ValueError(f"{head}; got dtype {x_scale.dtype}")
-    if x_scale.device != device:
-        raise ValueError(f"{head}; got a tensor on {x_scale.device}, the weight is on {device}")
-    if x_scale.dim() != 1 or int(x_scale.shape[0]) != words:
-        raise ValueError(f"{head}; got shape {list(x_scale.shape)}")
-    if x_scale.numel() > 0:
-        if not x_scale.is_contiguous():
-            raise ValueError(f"{head}; got strides {tuple(x_scale.stride())}")
-        if x_scale.data_ptr() % 16 != 0:
-            raise ValueError(f"{head}; its data pointer is not 16-byte aligned")
+        found = f"a {type(x_scale).__name__}"
+    elif x_scale.dtype != torch.int32:
+        found = f"dtype {x_scale.dtype}"
+    elif x_scale.device != device:
+        found = f"a tensor on {x_scale.device} (the weight is on {device})"
+    elif x_scale.dim() != 1 or int(x_scale.shape[0]) != words:
+        found = f"shape {list(x_scale.shape)}"
+    elif x_scale.numel() > 0 and not x_scale.is_contiguous():
+        found = f"strides {tuple(x_scale.stride())}"
+    elif x_scale.numel() > 0 and x_scale.data_ptr() % 16 != 0:
+        found = "a data pointer that is not a multiple of 16 bytes"
+    else:
+        return
+    raise ValueError(f"{op}: x_scale must be what activation contract v1 prescribes for an [M, K] = [{m}, {k}] "
+                     f"activation on this device, a contiguous 16-byte aligned int32 [{words}] tensor in the atom "
+                     f"layout; got {found}")
 
 
 def _x_bf16_storage(x):
@@ -455,14 +463,16 @@ def _dense_linear_quantized_fake(x, weight, scale, kind, bias=None, x_scale=None
 def _quantize_activation_checks(x, op: str) -> None:
     arch = device_arch()
     if arch // 10 != SERVED_MAJOR:
-        raise NotImplementedError(f"{op}: this device ({arch_label(arch)}) has no dense route in this build")
-    if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.dim() < 1:
-        got = f"{x.dtype} {tuple(x.shape)}" if isinstance(x, torch.Tensor) else type(x).__name__
-        raise ValueError(f"{op}: x must be bf16 [..., K], got {got}")
+        raise NotImplementedError(f"{op}: no dense route exists for this device ({arch_label(arch)}) in this build")
+    is_bf16 = isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and x.dim() >= 1
+    if not is_bf16:
+        what = f"{x.dtype} {tuple(x.shape)}" if isinstance(x, torch.Tensor) else type(x).__name__
+        raise ValueError(f"{op}: takes a bf16 [..., K] tensor, not {what}")
     if not x.is_cuda:
-        raise ValueError(f"{op}: x must be on the CUDA device, got {x.device}")
-    if x.shape[-1] % 128 != 0:
-        raise ValueError(f"{op}: K = {x.shape[-1]} is not a multiple of 128, which activation contract v1 requires")
+        raise ValueError(f"{op}: x is on {x.device}; it must be on the CUDA device")
+    k = int(x.shape[-1])
+    if k % 128 != 0:
+        raise ValueError(f"{op}: activation contract v1 needs K to be a multiple of 128 and K is {k}")
 
 
 @torch.library.custom_op(
@@ -491,44 +501,41 @@ def _dense_quantize_activation_fake(x):
 # ------------------------------------------------------------------------------------------------ public functions
 
 def _trim_none(*args) -> tuple:
-    args = list(args)
-    while args and args[-1] is None:
-        args.pop()
-    return tuple(args)
+    """The arguments without their trailing Nones (the ops' optional arguments default to None, so a call that
+    sets none of them records the short form in a traced graph)."""
+    keep = len(args)
+    while keep > 0 and args[keep - 1] is None:
+        keep -= 1
+    return tuple(args[:keep])
 
 
 def _check_handle(weight, where: str, ctx: str) -> None:
     if not isinstance(weight, DenseWeight):
-        raise TypeError(f"{ctx} ({where}): weight must be the DenseWeight handle from fso.dense.prepare_weight, got "
-                        f"{type(weight).__name__}")
+        raise TypeError(f"{ctx} ({where}): the weight argument is a {type(weight).__name__}; pass the DenseWeight that "
+                        f"fso.dense.prepare_weight returned")
     if weight.arch // 10 != device_arch() // 10:
-        raise ValueError(f"{ctx}: the weight was prepared on sm_{weight.arch} and this device is {where}")
+        raise ValueError(f"{ctx}: this weight was prepared for sm_{weight.arch}, the current device is {where}")
 
 
 def _flatten_x(x, weight, x_scale, where: str, ctx: str):
+    """(x as [M, K], the leading dimensions of the result). A bf16 x may have any leading dimensions; a
+    pre-quantized one is already the 2-D contiguous tensor of the activation contract."""
+    tag = f"{ctx} ({where}, kind {weight.kind!r})"
+    k = weight.in_features
+    is_tensor = isinstance(x, torch.Tensor)
+    shown = (f"{x.dtype} {tuple(x.shape)} strides {tuple(x.stride())}" if is_tensor else type(x).__name__)
     if x_scale is None:
-        if isinstance(x, torch.Tensor) and x.dtype == FP8:
-            raise ValueError(f"{ctx} ({where}, kind {weight.kind!r}): x is float8_e4m3fn but no x_scale was given")
-        if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.dim() < 1 \
-                or x.shape[-1] != weight.in_features:
-            got = f"{x.dtype} {tuple(x.shape)}" if isinstance(x, torch.Tensor) else type(x).__name__
-            raise ValueError(f"{ctx} ({where}, kind {weight.kind!r}): x must be bf16 [..., K] with K = in_features "
-                             f"= {weight.in_features}, got {got}")
-    else:
-        if not isinstance(x, torch.Tensor) or x.dtype != FP8 or x.dim() != 2 \
-                or x.shape[-1] != weight.in_features or not x.is_contiguous():
-            got = (f"{x.dtype} {tuple(x.shape)} strides {tuple(x.stride())}" if isinstance(x, torch.Tensor)
-                   else type(x).__name__)
-            raise ValueError(f"{ctx} ({where}, kind {weight.kind!r}): with x_scale, x must be the float8_e4m3fn "
-                             f"[M, K] activation of fso.dense.quantize_activation (2-D, contiguous, K = "
-                             f"{weight.in_features}), got {got}")
+        if is_tensor and x.dtype == FP8:
+            raise ValueError(f"{tag}: a float8_e4m3fn x needs its x_scale")
+        if not (is_tensor and x.dtype == torch.bfloat16 and x.dim() >= 1 and x.shape[-1] == k):
+            raise ValueError(f"{tag}: x must be bf16 [..., {k}] (K = in_features); got {shown}")
+    elif not (is_tensor and x.dtype == FP8 and x.dim() == 2 and x.shape[1] == k and x.is_contiguous()):
+        raise ValueError(f"{tag}: together with x_scale, x must be the contiguous float8_e4m3fn [M, {k}] tensor of "
+                         f"fso.dense.quantize_activation; got {shown}")
     if x.device != weight.weight.device:
-        raise ValueError(f"{ctx} ({where}, kind {weight.kind!r}): x is on {x.device} and the weight on "
-                         f"{weight.weight.device}")
+        raise ValueError(f"{tag}: x lives on {x.device}, the weight on {weight.weight.device}")
     lead = x.shape[:-1]
-    if x_scale is not None:
-        return x, lead
-    return x.reshape(-1, weight.in_features), lead
+    return (x if x_scale is not None else x.reshape(-1, k)), lead
 
 
 def linear(x, weight, *, bias=None, x_scale=None, residual=None, activation=None) -> torch.Tensor:
@@ -542,19 +549,21 @@ def linear(x, weight, *, bias=None, x_scale=None, residual=None, activation=None
     where = arch_label(device_arch())
     _check_handle(weight, where, "fso.dense.linear")
     x2, lead = _flatten_x(x, weight, x_scale, where, "fso.dense.linear")
-    r2 = None
+    n = weight.out_features
+    out_shape = tuple(lead) + (n,)
+    res2 = None
     if residual is not None:
-        want = tuple(lead) + (weight.out_features,)
-        if not isinstance(residual, torch.Tensor) or tuple(residual.shape) != want:
+        ok = isinstance(residual, torch.Tensor) and tuple(residual.shape) == out_shape
+        if not ok:
             got = list(residual.shape) if isinstance(residual, torch.Tensor) else type(residual).__name__
-            raise ValueError(f"fso.dense.linear ({where}, kind {weight.kind!r}): residual must have the result's "
-                             f"shape {list(want)}, got {got}")
+            raise ValueError(f"fso.dense.linear ({where}, kind {weight.kind!r}): the residual is added to the result "
+                             f"and must have its shape {list(out_shape)}; got {got}")
         if not residual.is_contiguous():
-            raise ValueError(f"fso.dense.linear ({where}, kind {weight.kind!r}): residual must be contiguous")
-        r2 = residual.view(-1, weight.out_features)
-    y = torch.ops.fish_scales_ops.dense_linear(
-        x2, weight.weight, weight.scale, weight.kind, *_trim_none(bias, x_scale, r2, activation))
-    return y.reshape(*lead, weight.out_features)
+            raise ValueError(f"fso.dense.linear ({where}, kind {weight.kind!r}): the residual must be contiguous")
+        res2 = residual.view(-1, n)
+    extra = _trim_none(bias, x_scale, res2, activation)
+    y = torch.ops.fish_scales_ops.dense_linear(x2, weight.weight, weight.scale, weight.kind, *extra)
+    return y.reshape(out_shape)
 
 
 def linear_quantized(x, weight, *, bias=None, x_scale=None, activation=None):

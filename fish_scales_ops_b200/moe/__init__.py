@@ -117,37 +117,40 @@ class MoeExperts:
 
 
 def _check_expert_tensors(w13, w2, fmt: str, where: str):
+    """(E, H, I) of a stacked expert pair after checking that the two tensors describe the same experts."""
     ctx = f"fso.moe.prepare_experts (format {fmt!r}, {where})"
-    for name, t in (("w13", w13), ("w2", w2)):
+    both = {"w13": w13, "w2": w2}
+    for name, t in both.items():
         if not isinstance(t, torch.Tensor):
-            raise ValueError(f"{ctx}: {name} must be a tensor, got {type(t).__name__}")
+            raise ValueError(f"{ctx}: {name} is a {type(t).__name__}, not a tensor")
+    for name, t in both.items():
         if t.dim() != 3:
-            raise ValueError(f"{ctx}: {name} must be 3-D, got shape {tuple(t.shape)}")
+            raise ValueError(f"{ctx}: {name} has shape {tuple(t.shape)}; experts are stacked along a leading "
+                             f"dimension ([E, 2*I, H] and [E, H, I])")
         if not t.is_cuda:
-            raise ValueError(f"{ctx}: {name} must be on the CUDA device that will serve the layer, got {t.device}")
-    if w2.device != w13.device:
-        raise ValueError(f"{ctx}: w13 is on {w13.device} and w2 on {w2.device}")
-    e, two_i, h = (int(v) for v in w13.shape)
-    e2, h2, i = (int(v) for v in w2.shape)
-    if e2 != e:
-        raise ValueError(f"{ctx}: w13 holds {e} experts and w2 {e2}")
-    if not 1 <= e <= 1024:
-        raise ValueError(f"{ctx}: {e} local experts; the routing kernels take 1 to 1024")
-    if h2 != h:
-        raise ValueError(f"{ctx}: w13 is [E, 2*I, {h}] but w2 is [E, {h2}, I]")
+            raise ValueError(f"{ctx}: {name} is on {t.device}; the experts must be on the CUDA device that runs the "
+                             f"layer")
+    if w13.device != w2.device:
+        raise ValueError(f"{ctx}: the two tensors are on different devices ({w13.device} and {w2.device})")
+    e, two_i, h = map(int, w13.shape)
+    e2, h2, i = map(int, w2.shape)
+    if e != e2:
+        raise ValueError(f"{ctx}: {e} experts in w13 but {e2} in w2")
+    if e < 1 or e > 1024:
+        raise ValueError(f"{ctx}: the routing kernels serve 1 to 1024 local experts, got {e}")
+    if h != h2:
+        raise ValueError(f"{ctx}: the hidden size differs between w13 [E, 2*I, {h}] and w2 [E, {h2}, I]")
     if two_i != 2 * i:
-        raise ValueError(f"{ctx}: w13 has {two_i} rows per expert and w2 contracts over {i}; w13 must stack gate and up")
-    if h % 128 != 0:
-        raise ValueError(f"{ctx}: hidden size {h} is not a multiple of 128")
-    if i % 128 != 0:
-        raise ValueError(f"{ctx}: intermediate size per rank I_local = {i} is not a multiple of 128")
+        raise ValueError(f"{ctx}: w13 must stack the gate and the up projection, 2*I = {2 * i} rows per expert for "
+                         f"w2's I = {i}; it has {two_i}")
+    for label, v in (("hidden size H", h), ("intermediate size I (per rank)", i)):
+        if v % 128 != 0:
+            raise ValueError(f"{ctx}: the {label} = {v} must be a multiple of 128")
     return e, h, i
 
 
 def _aligned_storage(t: torch.Tensor) -> torch.Tensor:
-    if t.numel() == 0 or t.data_ptr() % 16 == 0:
-        return t
-    return t.clone()
+    return t.clone() if t.numel() > 0 and t.data_ptr() % 16 != 0 else t
 
 
 def _interleave_perm(two_i: int, device) -> torch.Tensor:
@@ -423,64 +426,62 @@ def layer(hidden, experts, topk_ids, topk_w, *, bias=None, bias_scale=None) -> t
     arch = device_arch()
     where = arch_label(arch)
     if not isinstance(experts, MoeExperts):
-        raise TypeError(f"fso.moe.layer ({where}): experts must be the MoeExperts handle from "
-                        f"fso.moe.prepare_experts, got {type(experts).__name__}")
+        raise TypeError(f"fso.moe.layer ({where}): experts is a {type(experts).__name__}; pass the MoeExperts that "
+                        f"fso.moe.prepare_experts returned")
     if experts.arch // 10 != arch // 10:
-        raise ValueError(f"fso.moe.layer: the experts were prepared on sm_{experts.arch} and this device is {where}")
-    if not isinstance(hidden, torch.Tensor) or hidden.dim() != 2 or hidden.dtype != torch.bfloat16:
-        raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): hidden must be bf16 [M, H]")
+        raise ValueError(f"fso.moe.layer: these experts were prepared for sm_{experts.arch}, the current device is "
+                         f"{where}")
+    tag = f"fso.moe.layer ({where}, kind {experts.kind!r})"
+    h = experts.hidden
+    if not (isinstance(hidden, torch.Tensor) and hidden.dim() == 2 and hidden.dtype == torch.bfloat16):
+        raise ValueError(f"{tag}: hidden must be a bf16 [M, H] tensor")
     m = int(hidden.shape[0])
-    if int(hidden.shape[1]) != experts.hidden:
-        raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): hidden is [{m}, {int(hidden.shape[1])}] but "
-                         f"the experts span H = {experts.hidden}")
-    if not isinstance(topk_ids, torch.Tensor) or not isinstance(topk_w, torch.Tensor) or topk_ids.dim() != 2 \
-            or topk_w.dim() != 2 or tuple(topk_ids.shape) != tuple(topk_w.shape) or int(topk_ids.shape[0]) != m:
-        raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): topk_ids and topk_w must both be [M, topk] "
-                         f"with M = {m}")
+    if int(hidden.shape[1]) != h:
+        raise ValueError(f"{tag}: hidden has {int(hidden.shape[1])} columns, the experts were prepared for H = {h}")
+    routing_ok = (isinstance(topk_ids, torch.Tensor) and isinstance(topk_w, torch.Tensor) and topk_ids.dim() == 2
+                  and topk_ids.shape == topk_w.shape and int(topk_ids.shape[0]) == m)
+    if not routing_ok:
+        raise ValueError(f"{tag}: topk_ids and topk_w must be two [M, topk] tensors of one shape, M = {m}")
     if topk_ids.dtype not in (torch.int32, torch.int64):
-        raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): topk_ids must be int32 or int64, got "
-                         f"{topk_ids.dtype}")
+        raise ValueError(f"{tag}: topk_ids is {topk_ids.dtype}; expert ids are int32 or int64")
     if not topk_w.is_floating_point():
-        raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): topk_w must be floating point, got "
-                         f"{topk_w.dtype}")
-    ids = (topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)).contiguous()
-    wts = (topk_w if topk_w.dtype == torch.float32 else topk_w.to(torch.float32)).contiguous()
-    x = hidden if hidden.is_contiguous() else hidden.contiguous()
-    if bias is not None:
-        if bias.dim() != 2 or tuple(bias.shape) != (m, experts.hidden) or bias.dtype != torch.bfloat16:
-            raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): bias must be bf16 [{m}, "
-                             f"{experts.hidden}], got {bias.dtype} {tuple(bias.shape)}")
-        bias = bias.contiguous()
+        raise ValueError(f"{tag}: topk_w is {topk_w.dtype}; routing weights are floating point")
+    if bias is not None and not (bias.dim() == 2 and tuple(bias.shape) == (m, h) and bias.dtype == torch.bfloat16):
+        raise ValueError(f"{tag}: bias must be bf16 [{m}, {h}]; got {bias.dtype} {tuple(bias.shape)}")
     if bias_scale is not None:
         if bias is None:
-            raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): bias_scale scales bias and needs it")
+            raise ValueError(f"{tag}: bias_scale multiplies bias and cannot be given without it")
         if bias_scale.numel() != m or not bias_scale.is_floating_point():
-            raise ValueError(f"fso.moe.layer ({where}, kind {experts.kind!r}): bias_scale must hold one "
-                             f"floating-point factor per token ({m})")
+            raise ValueError(f"{tag}: bias_scale must be one floating-point factor per token ({m} of them)")
         bias_scale = bias_scale.reshape(m).to(torch.float32).contiguous()
-    return torch.ops.fish_scales_ops.moe_layer(x, experts.w13, experts.sw13, experts.w2, experts.sw2, ids, wts, bias,
-                                               bias_scale, experts.kind, experts.w13_interleaved)
+    ids = topk_ids.to(torch.int32).contiguous()
+    wts = topk_w.to(torch.float32).contiguous()
+    return torch.ops.fish_scales_ops.moe_layer(hidden.contiguous(), experts.w13, experts.sw13, experts.w2, experts.sw2,
+                                               ids, wts, None if bias is None else bias.contiguous(), bias_scale,
+                                               experts.kind, experts.w13_interleaved)
 
 
 def transient_bytes(experts, tokens, topk) -> int:
     """Device memory, in bytes, one :func:`layer` call with ``tokens`` rows allocates: the routing tensors, the
-    shared gather / down-projection region, the FC1 output and its scales and the result, each charged as the
-    caching allocator can charge it. The layer and this function read the same plan
-    (python/fish_scales_ops/moe/__init__.py:816-870)."""
+    shared gather / down-projection region, the FC1 output and its scales (in the decode band also its fp32 gate / up
+    accumulators) and the result, each charged as the caching allocator can charge it. The layer and this function
+    read the same plan (python/fish_scales_ops/moe/__init__.py:816-870)."""
     arch = device_arch()
     where = arch_label(arch)
     if not isinstance(experts, MoeExperts):
-        raise TypeError(f"fso.moe.transient_bytes ({where}): experts must be the MoeExperts handle from "
-                        f"fso.moe.prepare_experts, got {type(experts).__name__}")
+        raise TypeError(f"fso.moe.transient_bytes ({where}): experts is a {type(experts).__name__}; pass the "
+                        f"MoeExperts that fso.moe.prepare_experts returned")
     if experts.arch // 10 != arch // 10:
-        raise ValueError(f"fso.moe.transient_bytes: the experts were prepared on sm_{experts.arch} and this device is "
-                         f"{where}")
-    for name, v in (("tokens", tokens), ("topk", topk)):
-        if not isinstance(v, int) or isinstance(v, bool) or v < 0:
-            raise ValueError(f"fso.moe.transient_bytes ({where}): {name} must be a non-negative int, got {v!r}")
+        raise ValueError(f"fso.moe.transient_bytes: these experts were prepared for sm_{experts.arch}, the current "
+                         f"device is {where}")
+    counts = {"tokens": tokens, "topk": topk}
+    for name, v in counts.items():
+        if isinstance(v, bool) or not isinstance(v, int) or v < 0:
+            raise ValueError(f"fso.moe.transient_bytes ({where}): {name} = {v!r} is not a non-negative int")
     if tokens == 0:
         return 0
-    if topk < 1:
-        raise ValueError(f"fso.moe.transient_bytes ({where}): topk must be >= 1, got {topk}")
+    if topk == 0:
+        raise ValueError(f"fso.moe.transient_bytes ({where}): a call with tokens routes each of them to at least one "
+                         f"expert (topk >= 1)")
     plan = _layer_plan(tokens, topk, experts.num_experts, experts.hidden, experts.inter)
     return _plan_bytes(plan, tokens, experts.num_experts, experts.hidden, experts.inter)

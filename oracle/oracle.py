@@ -26,8 +26,14 @@ _p = ctypes.c_void_p
 
 
 def build():
-    """Compile the checker (and, where the reference tree is present, the reference-header shim)."""
-    subprocess.run(["make", "-C", _HERE, "-s"], check=True, stdout=subprocess.DEVNULL)
+    """Compile the checker (and, where the reference tree is present, the reference-header shim). The reference tree
+    is the one FSO_REFERENCE_ROOT names, else a directory called ``reference`` beside this repository."""
+    env = dict(os.environ)
+    if not env.get("FSO_REFERENCE_ROOT"):
+        beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+        if os.path.isdir(beside):
+            env["FSO_REFERENCE_ROOT"] = beside
+    subprocess.run(["make", "-C", _HERE, "-s"], check=True, stdout=subprocess.DEVNULL, env=env)
 
 
 def lib():
