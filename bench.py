@@ -149,12 +149,16 @@ def shared_dist(torch) -> "Dist":
     return _SHARED_DIST
 
 
-def timed_steps(torch, d: Dist, step, steps: int, warmup: int, per_step_events: bool = False):
+def timed_steps(torch, d: Dist, step, steps: int, warmup: int, per_step_events: bool = False, finish=None):
     """W untimed steps, then exactly K steps between barrier + synchronize on both sides, timed with CUDA events on
-    the launching stream. Returns (total ms, clocks summary, [per-step event pairs])."""
+    the launching stream. ``finish`` (optional) runs after the last step and before the closing event: it makes the
+    launching stream wait for work the steps put on other streams. Returns (total ms, clocks summary, [per-step
+    event pairs])."""
     stream = torch.cuda.current_stream()
     for _ in range(warmup):
         step(None)
+    if finish is not None:
+        finish()
     d.barrier()
     pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)] \
         if per_step_events else None
@@ -164,9 +168,49 @@ def timed_steps(torch, d: Dist, step, steps: int, warmup: int, per_step_events: 
         t0.record(stream)
         for i in range(steps):
             step(pairs[i] if pairs else None)
+        if finish is not None:
+            finish()
         t1.record(stream)
         d.barrier()
     return t0.elapsed_time(t1), clocks.summary(), pairs
+
+
+class HostPipeline:
+    """End-to-end steps with host buffers: every step copies its input from pinned host memory to the device, runs
+    ``fn`` on it (the public call) and copies the result back to pinned host memory. The three legs run on three
+    streams with two input buffers, so step i's result leaves over PCIe while step i + 1's input arrives and its
+    kernels run; every byte of every step still moves inside the timed region."""
+
+    def __init__(self, torch, x_host, fn, out_host):
+        self.torch, self.fn, self.x_host, self.out_host = torch, fn, x_host, out_host
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.x_dev = [torch.empty(x_host.shape, dtype=x_host.dtype, device="cuda") for _ in range(2)]
+        self.x_free = [None, None]          # event after which x_dev[j] may be overwritten
+        self.out_done = None
+        self.i = 0
+
+    def step(self, _):
+        torch, j = self.torch, self.i % 2
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(self.s_in):
+            if self.x_free[j] is not None:
+                self.s_in.wait_event(self.x_free[j])
+            self.x_dev[j].copy_(self.x_host, non_blocking=True)
+            arrived = self.s_in.record_event()
+        main.wait_event(arrived)
+        y = self.fn(self.x_dev[j])
+        computed = main.record_event()
+        self.x_free[j] = computed
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(computed)
+            self.out_host.copy_(y, non_blocking=True)
+            y.record_stream(self.s_out)
+            self.out_done = self.s_out.record_event()
+        self.i += 1
+
+    def finish(self):
+        if self.out_done is not None:
+            self.torch.cuda.current_stream().wait_event(self.out_done)
 
 
 def base_line(args, d, metric, unit, value, ms_step, scaling, dtype, config):
@@ -285,13 +329,11 @@ def dense_ours(args):
     ms_total, clocks, pairs = timed_steps(torch, d, step, args.steps, args.warmup, per_step_events=True)
     gemm_ms = sum(a.elapsed_time(b) for a, b in pairs) / args.steps
 
-    # end to end through the public call with host buffers: H2D of the activation, linear, D2H of the result
-    def e2e_step(_):
-        xd = x_host.to("cuda", non_blocking=True)
-        y_host.copy_(fso.dense.linear(xd, weight), non_blocking=True)
-
+    # end to end through the public call with host buffers: H2D of the activation, linear, D2H of the result, every
+    # step; the copies of neighbouring steps overlap (PCIe is full duplex), the kernels of one step do not move
+    pipe = HostPipeline(torch, x_host, lambda xd: fso.dense.linear(xd, weight), y_host)
     e_steps = max(3, min(args.steps, 20))
-    e2e_ms, _, _ = timed_steps(torch, d, e2e_step, e_steps, 2)
+    e2e_ms, _, _ = timed_steps(torch, d, pipe.step, e_steps, 2, finish=pipe.finish)
     # sustained: back-to-back steps for at least two seconds (the timed K steps above are a burst of a few tens of
     # milliseconds; under the 1 kW cap the part settles at a lower clock)
     sus_steps = max(args.steps, int(2.2e3 / max(ms_total / args.steps, 1e-3)))
@@ -517,11 +559,14 @@ def moe_ours(args):
 
     ms_total, clocks, _ = timed_steps(torch, d, lambda _: run(hidden), args.steps, args.warmup)
 
-    def e2e_step(_):
-        out_host.copy_(run(hidden_host.to("cuda", non_blocking=True)), non_blocking=True)
-
+    pipe = HostPipeline(torch, hidden_host, run, out_host)
     e_steps = max(3, min(args.steps, 10))
-    e2e_ms, _, _ = timed_steps(torch, d, e2e_step, e_steps, 2)
+    e2e_ms, _, _ = timed_steps(torch, d, pipe.step, e_steps, 2, finish=pipe.finish)
+    # small batches are launch-bound when issued eagerly: the device time of one layer under CUDA-graph replay (the
+    # reference's own protocol, bench/gemm/python/bench_moe_qwen3_30a3.py:748-811) is reported beside the eager step
+    replay_us = None
+    if d.world == 1 and tokens <= 1024:
+        replay_us = graph_replay_us(torch, lambda i: run(hidden), 1, max(10, args.steps))
     ms_total, e2e_ms = d.max_over_ranks([ms_total, e2e_ms])
     status = _ops.device_status()
     # correctness of what was timed: rank 0's first tokens against the CPU oracle (every N), and under expert
@@ -591,6 +636,12 @@ def moe_ours(args):
                                           f"quantized ({dt:.2f} s)"}
     if transports_equal is not None:
         line["transports_bit_equal"] = transports_equal
+    if replay_us is not None:
+        live = len({int(v) for v in ids_cpu.reshape(-1).tolist()})
+        live_bytes = live * 3 * cfg["H"] * cfg["I"] * (1 + 1 / 32)
+        line["graph_replay"] = {"us_per_layer": replay_us, "tokens_per_s": tokens / (replay_us * 1e-6),
+                                "experts_in_use": live, "live_weight_bytes": live_bytes,
+                                "frac_of_measured_hbm": live_bytes / (replay_us * 1e-6) / (pk["hbm_gbs"] * 1e9)}
     d.close()
     return line
 
@@ -858,6 +909,18 @@ def main():
                     sub_line = moe_ours(ex)
                     line[name] = {k: sub_line[k] for k in keys if k in sub_line}
                     torch.cuda.empty_cache()
+                # the decode band (BASELINE.json configs[3] at T in {1, 64}, and DeepSeek-V3 at 64 tokens): device time
+                # of one layer under CUDA-graph replay against the stream of the live experts' weights
+                ex.skew, ex.steps = 0.0, 30
+                cells = {}
+                for cfg_name, tok in (("mixtral", 1), ("mixtral", 64), ("dsv3", 64)):
+                    ex.moe_config, ex.moe_tokens = cfg_name, tok
+                    sub_line = moe_ours(ex)
+                    cells[f"{cfg_name}_t{tok}"] = {"eager_ms_per_step": sub_line["ms_per_step"], **sub_line["graph_replay"]}
+                    torch.cuda.empty_cache()
+                line["moe_decode"] = {"metric": "moe_layer_graph_replay_us", "cells": cells,
+                                      "note": "calls of at most 64 tokens; weights of the experts in use on MMA-M "
+                                              "where the band rule picks the decode kernels"}
             d.keep = False
             d.close()
     if line is not None:

@@ -88,7 +88,14 @@ struct GemmCfg {
     // slice fits in registers and the accumulator can be handed back before the activation math starts.
     static constexpr int kEpiWarps = EPI == 2 /* EPI_SWIGLU */ ? 16 : BN >= 128 ? 8 : 4;
     static constexpr int kThreads = 128 + 32 * kEpiWarps;
-    static constexpr int kAccStages = BN == 256 ? 1 : 2;
+    // Two accumulators, drained by the epilogue while the next tile's MMAs fill the other one. 2 x 256 columns plus
+    // the scale-factor buffers do not fit in the 512 columns of tensor memory, so at BN = 256 the two accumulators
+    // share 32 columns: accumulator 0 is columns [0, 256), accumulator 1 is [224, 480). The epilogue of a tile
+    // drains the shared columns first and signals a barrier of their own; the MMAs of the next tile wait for that
+    // barrier only (and for the complete drain of the tile before, which used the same accumulator).
+    static constexpr bool kOverlapAcc = BN == 256;
+    static constexpr int kAccStages = 2;
+    static constexpr int kAccStride = kOverlapAcc ? 224 : BN;
     static constexpr int kABytes = kBM * kBK;
     static constexpr int kBBytes = BN * kBK;
     static constexpr int kSfaBytes = 512;
@@ -107,7 +114,7 @@ struct GemmCfg {
     // buffers once its own main loop is over
     static constexpr int kRedSlices = (kStages * kStageBytes) / (BN * 512);
     // tensor-memory columns: accumulators first, then two alternating scale-factor buffers
-    static constexpr int kAccCols = kAccStages * BN;
+    static constexpr int kAccCols = kAccStride * (kAccStages - 1) + BN;
     static constexpr int kSfaCols = 4;
     static constexpr int kSfbCols = 4 * kSfbAtoms;
     static constexpr int kSfBufCols = kSfaCols + kSfbCols;
@@ -223,7 +230,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * S + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * S + 2 + a); };
-    uint32_t const misc_off = static_cast<uint32_t>(S) * C::kStageBytes + 8u * (2 * S + 4);
+    uint32_t const ovl_bar = bars + 8u * (2 * S + 4);      // the columns both accumulators use have been drained
+    uint32_t const misc_off = static_cast<uint32_t>(S) * C::kStageBytes + 8u * (2 * S + 5);
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(gbase + misc_off);
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(gbase + misc_off + 4);
     constexpr uint32_t red_off = 0;       // EPI_CLUSTER: the other slices' accumulators reuse the stage buffers
@@ -233,7 +241,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     bool red_have = false;
     TileCoord red_c{};
 
-    int const warp = threadIdx.x >> 5;
+    // broadcast from lane 0: the compiler then knows the warp index (and every branch on it) to be warp-uniform
+    int const warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     int const lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -245,6 +254,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), C::kEpiWarps);
         }
+        mbar_init(ovl_bar, 4);
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_tensormap(&tm_a);
@@ -279,7 +289,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
             TileCoord c;
@@ -355,12 +365,13 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             int sfbuf = 0;
+            int tiles_done = 0;
             constexpr uint32_t idesc = make_idesc_mxf8(BN);
             TileCoord c;
             bool ok = true;
@@ -374,8 +385,16 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
                     break;
                 }
+                if constexpr (C::kOverlapAcc) {
+                    // the tile before this one sits in the other accumulator: its shared columns must have left
+                    if (tiles_done > 0 && !wait_or_abort(ovl_bar, static_cast<uint32_t>(tiles_done - 1) & 1u, abort_flag)) {
+                        record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
+                        break;
+                    }
+                }
+                ++tiles_done;
                 tc_fence_after();
-                uint32_t const d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                uint32_t const d_tmem = tmem_base + static_cast<uint32_t>(acc * C::kAccStride);
                 uint32_t const sfb_col_off = kGS ? static_cast<uint32_t>((c.sub * BN) >> 5)
                     : BN < 128 ? static_cast<uint32_t>(((c.b_tile * BN) & 127) >> 5) : 0u;
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -433,8 +452,21 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
             tc_fence_after();
             uint32_t const t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16)
-                + static_cast<uint32_t>(acc * BN);
+                + static_cast<uint32_t>(acc * C::kAccStride);
             int const a_row = c.a_tile * C::kBM + quarter * 32 + lane;   // this thread's row of the MMA-M operand
+            // Overlapping accumulators: the 32 shared columns are the last 32 of accumulator 0 and the first 32 of
+            // accumulator 1. A warp walks its 32-column chunks from the end in accumulator 0 and from the start in
+            // accumulator 1, so the warps whose slice holds the shared columns drain them first and say so.
+            constexpr int kSlices = C::kEpiWarps / 4;
+            bool const rev = C::kOverlapAcc && acc == 0;
+            bool const ovl_owner = C::kOverlapAcc && half == (acc == 0 ? kSlices - 1 : 0);
+            auto release_shared_columns = [&]() {
+                if (ovl_owner) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ovl_bar);
+                }
+            };
             int const b_row0 = kGS ? c.b_tile * 128 + c.sub * BN : c.b_tile * BN;
             int const b_bound = kGS ? b_row0 + c.live : p.rows_b;        // swapped: first token row past this tile's
             bool released = false;
@@ -460,6 +492,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 tmem_ld_32x32(t_row + half * 64, r0);
                 tmem_ld_32x32(t_row + half * 64 + 32, r1);
                 tmem_ld_wait();
+                release_shared_columns();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -503,59 +536,65 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             } else if constexpr (!kSwap && EPI == EPI_BF16) {
                 // row = output row, columns = output columns. The accumulator slice is drained into packed bf16
                 // registers first and handed back to the MMA issuer; the global stores then overlap the next tile.
-                constexpr int kPacked = kColsPerWarp / 2;
-                uint32_t packed[kPacked];
+                constexpr int kChunks = kColsPerWarp / 32;
+                static_assert(kChunks % 2 == 0, "chunks are drained two at a time");
+                uint32_t packed[kChunks * 16];
+                int const col_w = b_row0 + half * kColsPerWarp;          // first output column of this warp
+                auto chunk_col = [&](int j) { return 32 * (rev ? kChunks - 1 - j : j); };
+                auto load_chunk = [&](int j, uint32_t (&r)[32]) {
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(half * kColsPerWarp + chunk_col(j)), r);
+                };
+                // bias per column (the same for every row: broadcast loads), residual from this row
+                auto fuse32 = [&](uint32_t (&r)[32], int col) {
+                    if (col >= p.rows_b) return;
+                    bool const has_bias = p.bias != nullptr;
+                    bool const has_res = p.residual != nullptr && a_row < p.rows_a;
 #pragma unroll
-                for (int c0 = 0; c0 < kColsPerWarp; c0 += 64) {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld_32x32(t_row + half * kColsPerWarp + c0, r0);
-                    if (c0 + 32 < kColsPerWarp) tmem_ld_32x32(t_row + half * kColsPerWarp + c0 + 32, r1);
-                    tmem_ld_wait();
-                    if constexpr (kFused) {
-                        // bias per column (the same for every row: broadcast loads), residual from this row
-                        int const col0 = b_row0 + half * kColsPerWarp + c0;
-                        auto fuse32 = [&](uint32_t (&r)[32], int col) {
-                            if (col >= p.rows_b) return;
-                            bool const has_bias = p.bias != nullptr;
-                            bool const has_res = p.residual != nullptr && a_row < p.rows_a;
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 bw = make_uint4(0, 0, 0, 0), rw = make_uint4(0, 0, 0, 0);
+                        if (has_bias) bw = __ldg(reinterpret_cast<const uint4*>(p.bias + col + 8 * q));
+                        if (has_res)
+                            rw = __ldg(reinterpret_cast<const uint4*>(
+                                p.residual + static_cast<int64_t>(a_row) * p.ldo + col + 8 * q));
+                        uint32_t const bws[4] = {bw.x, bw.y, bw.z, bw.w};
+                        uint32_t const rws[4] = {rw.x, rw.y, rw.z, rw.w};
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                uint4 bw = make_uint4(0, 0, 0, 0), rw = make_uint4(0, 0, 0, 0);
-                                if (has_bias) bw = __ldg(reinterpret_cast<const uint4*>(p.bias + col + 8 * q));
-                                if (has_res)
-                                    rw = __ldg(reinterpret_cast<const uint4*>(
-                                        p.residual + static_cast<int64_t>(a_row) * p.ldo + col + 8 * q));
-                                uint32_t const bws[4] = {bw.x, bw.y, bw.z, bw.w};
-                                uint32_t const rws[4] = {rw.x, rw.y, rw.z, rw.w};
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    float lo = epilogue_value(__uint_as_float(r[8 * q + 2 * i]),
-                                        bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] & 0xFFFFu))),
-                                        has_bias, p.act);
-                                    float hi = epilogue_value(__uint_as_float(r[8 * q + 2 * i + 1]),
-                                        bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] >> 16))),
-                                        has_bias, p.act);
-                                    if (has_res) {
-                                        lo += bf16_lo(rws[i]);
-                                        hi += bf16_hi(rws[i]);
-                                    }
-                                    r[8 * q + 2 * i] = __float_as_uint(lo);
-                                    r[8 * q + 2 * i + 1] = __float_as_uint(hi);
-                                }
+                        for (int i = 0; i < 4; ++i) {
+                            float lo = epilogue_value(__uint_as_float(r[8 * q + 2 * i]),
+                                bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] & 0xFFFFu))),
+                                has_bias, p.act);
+                            float hi = epilogue_value(__uint_as_float(r[8 * q + 2 * i + 1]),
+                                bias_term(__ushort_as_bfloat16(static_cast<unsigned short>(bws[i] >> 16))),
+                                has_bias, p.act);
+                            if (has_res) {
+                                lo += bf16_lo(rws[i]);
+                                hi += bf16_hi(rws[i]);
                             }
-                        };
-                        fuse32(r0, col0);
-                        if (c0 + 32 < kColsPerWarp) fuse32(r1, col0 + 32);
+                            r[8 * q + 2 * i] = __float_as_uint(lo);
+                            r[8 * q + 2 * i + 1] = __float_as_uint(hi);
+                        }
                     }
+                };
+                uint32_t ra[32], rb[32];
+                load_chunk(0, ra);
+                tmem_ld_wait();
+                release_shared_columns();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        packed[c0 / 2 + j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-                    if (c0 + 32 < kColsPerWarp) {
+                for (int j = 0; j < kChunks; j += 2) {
+                    // one load in flight while the chunk before it is packed
+                    load_chunk(j + 1, rb);
+                    if constexpr (kFused) fuse32(ra, col_w + chunk_col(j));
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            packed[c0 / 2 + 16 + j]
-                                = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-                    }
+                    for (int i = 0; i < 16; ++i)
+                        packed[16 * j + i] = pack_bf16x2(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1]));
+                    tmem_ld_wait();
+                    if (j + 2 < kChunks) load_chunk(j + 2, ra);
+                    if constexpr (kFused) fuse32(rb, col_w + chunk_col(j + 1));
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        packed[16 * (j + 1) + i]
+                            = pack_bf16x2(__uint_as_float(rb[2 * i]), __uint_as_float(rb[2 * i + 1]));
+                    if (j + 2 < kChunks) tmem_ld_wait();
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -563,11 +602,12 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 released = true;
                 if (a_row < p.rows_a) {
                     __nv_bfloat16* const orow = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(a_row) * p.ldo
-                        + b_row0 + half * kColsPerWarp;
+                        + col_w;
 #pragma unroll
-                    for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
-                        if (b_row0 + half * kColsPerWarp + c0 < p.rows_b) {
-                            uint32_t const* v = &packed[c0 / 2];
+                    for (int g = 0; g < 2 * kChunks; ++g) {
+                        int const c0 = chunk_col(g >> 1) + 16 * (g & 1);
+                        if (col_w + c0 < p.rows_b) {
+                            uint32_t const* v = &packed[8 * g];
                             if (p.out_align32) {
                                 asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                                              ::"l"(orow + c0), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]),
@@ -587,11 +627,15 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t codes[kColsPerWarp / 4];
                 uint32_t word = 0;
                 int const col_w = b_row0 + half * kColsPerWarp;          // first output column of this warp
+                constexpr int kChunks = kColsPerWarp / 32;
+                auto chunk_col = [&](int j) { return 32 * (rev ? kChunks - 1 - j : j); };
 #pragma unroll
-                for (int c0 = 0; c0 < kColsPerWarp; c0 += 32) {
+                for (int j = 0; j < kChunks; ++j) {
+                    int const c0 = chunk_col(j);
                     uint32_t r[32];
-                    tmem_ld_32x32(t_row + half * kColsPerWarp + c0, r);
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(half * kColsPerWarp + c0), r);
                     tmem_ld_wait();
+                    if (j == 0) release_shared_columns();
                     if constexpr (kFused) {
                         if (col_w + c0 < p.rows_b) {
                             bool const has_bias = p.bias != nullptr;
@@ -616,16 +660,16 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     float v[32];
                     float amax = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        v[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));   // the bf16 output's value
-                        amax = fmaxf(amax, fabsf(v[j]));
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));   // the bf16 output's value
+                        amax = fmaxf(amax, fabsf(v[i]));
                     }
                     amax = fmaxf(amax, 1e-10f);
                     float qs;
                     word |= e8m0_from_amax(amax, qs) << (8 * (c0 / 32));
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
-                        codes[c0 / 4 + q] = fp8x4(__fmul_rn(v[4 * q], qs), __fmul_rn(v[4 * q + 1], qs),
+                        codes[8 * j + q] = fp8x4(__fmul_rn(v[4 * q], qs), __fmul_rn(v[4 * q + 1], qs),
                             __fmul_rn(v[4 * q + 2], qs), __fmul_rn(v[4 * q + 3], qs));
                 }
                 tc_fence_before();
@@ -638,8 +682,9 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (a_row < p.rows_a) {
                         uint8_t* const dst = static_cast<uint8_t*>(p.out) + static_cast<int64_t>(a_row) * p.ldo + col_w;
 #pragma unroll
-                        for (int c0 = 0; c0 < kColsPerWarp; c0 += 32) {
-                            uint32_t const* o = &codes[c0 / 4];
+                        for (int j = 0; j < kChunks; ++j) {
+                            int const c0 = chunk_col(j);
+                            uint32_t const* o = &codes[8 * j];
                             if (p.out_align32) {
                                 asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                                              ::"l"(dst + c0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]),
@@ -660,11 +705,14 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             } else if constexpr (!kSwap) {
                 // split-K partial, normal orientation: fp32 rows straight from tensor memory
+                constexpr int kChunks = kColsPerWarp / 32;
 #pragma unroll 1
-                for (int c0 = half * kColsPerWarp; c0 < (half + 1) * kColsPerWarp; c0 += 32) {
+                for (int j = 0; j < kChunks; ++j) {
+                    int const c0 = half * kColsPerWarp + 32 * (rev ? kChunks - 1 - j : j);
                     uint32_t r[32];
-                    tmem_ld_32x32(t_row + c0, r);
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
                     tmem_ld_wait();
+                    if (j == 0) release_shared_columns();
                     int const col = b_row0 + c0;
                     if (a_row < p.rows_a && col < p.rows_b) {
                         uint4* dst = reinterpret_cast<uint4*>(p.ws + static_cast<int64_t>(c.split) * p.out_rows * p.ldo
