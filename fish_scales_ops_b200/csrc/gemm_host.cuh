@@ -301,14 +301,14 @@ inline int make_sf_map(CUtensorMap* map, const void* base, int64_t atoms)
     return 0;
 }
 
-// The CTA-pair kernel (gemm2.cuh) is opt-in: FSO_B200_PAIR=1 sends normal-orientation calls without split-K whose
-// 256 x 256 tiles fill the SM pairs to it (read once per process). It is bit-identical to the single-CTA kernel and
-// measured 4-6 % slower on B200, so the default keeps every call on the single-CTA kernel.
+// The CTA-pair kernel (gemm2.cuh) takes the normal-orientation calls without split-K and without a fused epilogue
+// whose 256 x 256 tiles fill the SM pairs; it is bit-identical to the single-CTA kernel and a few per cent faster on
+// those shapes on B200. FSO_B200_PAIR=0 keeps every call on the single-CTA kernel (read once per process).
 inline bool pair_kernel_enabled()
 {
     static int const v = [] {
         const char* e = std::getenv("FSO_B200_PAIR");
-        return (e != nullptr && e[0] != '0' && e[0] != '\0') ? 1 : 0;
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
     }();
     return v != 0;
 }
@@ -316,6 +316,10 @@ inline bool pair_kernel_enabled()
 inline bool use_pair_kernel(int64_t m, int64_t n, int sms, bool swap, int splits)
 {
     if (swap || splits != 1 || n % 256 != 0 || !pair_kernel_enabled()) return false;
+    // an odd number of 128-row blocks leaves the second CTA of the last pair without rows: only when that is a
+    // small part of the work
+    int64_t const blocks = (m + 127) / 128;
+    if (blocks % 2 != 0 && blocks < 15) return false;
     int64_t const tiles = ((m + 255) / 256) * (n / 256);
     return tiles >= sms / 2;
 }

@@ -256,8 +256,8 @@ def _outputs_in_child_process(shapes, env_extra, tag):
 
 
 def test_cta_pair_kernel_in_child_process(fso, device_ok):
-    """The opt-in CTA-pair kernel (FSO_B200_PAIR=1) gives the bytes of the single-CTA kernel, including a ragged M
-    whose second CTA of the last pair has no rows."""
+    """The CTA-pair kernel (large calls take it unless FSO_B200_PAIR=0) gives the bytes of the single-CTA kernel,
+    including a ragged M whose second CTA of the last pair has no rows."""
     shapes = ((2048, 4096, 512), (1920, 5120, 256), (2100, 4096, 1024))
     pair = _outputs_in_child_process(shapes, {"FSO_B200_PAIR": "1"}, "pair1")
     single = _outputs_in_child_process(shapes, {"FSO_B200_PAIR": "0"}, "pair0")
