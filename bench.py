@@ -361,16 +361,19 @@ def dense_ours(args):
     gemm_tflops = 2.0 * m * n_local * k / (gemm_ms * 1e-3) / 1e12
     line = base_line(args, d, "mxfp8_gemm_tflops", "TFLOP/s", flops / (ms_step * 1e-3) / 1e12, ms_step, "strong",
                      "fp8_e4m3", dense_config(m, n, k, d.world))
-    # DRAM traffic of one launch: the ncu capture of the same kernel on 8192 x 8192 x 4096 read + wrote 193.4 MB for
-    # 203.4 MB of algorithmic bytes (every operand byte fetched once, re-reads served by L2); the kernel's traffic
-    # grows in proportion to its algorithmic bytes, so the captured ratio is applied to this launch's bytes
+    # DRAM traffic of one launch: the ncu captures of the two kernels on 8192 x 8192 x 4096 (203.4 MB of algorithmic
+    # bytes) read + wrote 238.5 MB (pair kernel) and 193.4 MB (single-CTA kernel): operands fetched from HBM once or
+    # twice, re-reads served by L2, the output written once. The kernel's traffic grows in proportion to its
+    # algorithmic bytes, so the captured ratio is applied to this launch's bytes
+    kernel_name = dense_kernel_name(m, n_local)
+    captured_mb = 238.5 if "pair" in kernel_name else 193.4
     algo_bytes = (m * k + n_local * k) * (1 + 1 / 32) + 2.0 * m * n_local
     line["roofline"] = {
-        "bound": "tensor", "kernel": dense_kernel_name(m, n_local), "achieved": gemm_tflops, "peak": fp8_peak,
-        "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": algo_bytes * (193.4 / 203.4),
+        "bound": "tensor", "kernel": kernel_name, "achieved": gemm_tflops, "peak": fp8_peak,
+        "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": algo_bytes * (captured_mb / 203.4),
         "traffic_unit": "bytes per launch",
         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture on 8192x8192x4096 "
-                          "(193.4 MB for 203.4 MB algorithmic), scaled by this launch's algorithmic bytes "
+                          f"({captured_mb} MB for 203.4 MB algorithmic), scaled by this launch's algorithmic bytes "
                           f"({algo_bytes / 1e6:.1f} MB)",
         "peak_source": f"2 x {pk['source']} bf16 burst ({pk['bf16_burst']} TF/s): an fp8 MMA does twice the bf16 "
                        f"work per cycle; nominal dense fp8 is 4500",
