@@ -580,6 +580,9 @@ def moe_ours(args):
     replay_us = None
     if d.world == 1 and tokens <= 1024:
         replay_us = graph_replay_us(torch, lambda i: run(hidden), 1, max(10, args.steps))
+    stages = None
+    if d.world == 1 and getattr(args, "stages", False):
+        stages = moe_stage_times(torch, _ops, hidden, experts, ids, wts, max(5, min(args.steps, 20)))
     ms_total, e2e_ms = d.max_over_ranks([ms_total, e2e_ms])
     status = _ops.device_status()
     # correctness of what was timed: rank 0's first tokens against the CPU oracle (every N), and under expert
@@ -631,6 +634,8 @@ def moe_ours(args):
     # own kernels per step: route (3, or 1 for small batches), gather, FC1, FC2, combine; under expert parallelism
     # also the two plan kernels, the quantizer, the dispatch kernel and the final reduction
     per_step = 7 if tokens * cfg["k"] > 1024 else 5
+    if d.world == 1 and fso.moe._decode_band(tokens, cfg["k"], cfg["E"], cfg["I"])[0]:
+        per_step += 1          # decode band: FC1 leaves fp32 accumulators, a row-wise SiLU(gate)*up requantizer follows
     if d.world > 1 and ep_transport.startswith("peer"):
         per_step += 5
     elif d.world > 1:
@@ -649,6 +654,8 @@ def moe_ours(args):
                                           f"quantized ({dt:.2f} s)"}
     if transports_equal is not None:
         line["transports_bit_equal"] = transports_equal
+    if stages is not None:
+        line["stages"] = stages
     if replay_us is not None:
         live = len({int(v) for v in ids_cpu.reshape(-1).tolist()})
         live_bytes = live * 3 * cfg["H"] * cfg["I"] * (1 + 1 / 32)
@@ -657,6 +664,35 @@ def moe_ours(args):
                                 "frac_of_measured_hbm": live_bytes / (replay_us * 1e-6) / (pk["hbm_gbs"] * 1e9)}
     d.close()
     return line
+
+
+def moe_stage_times(torch, _ops, hidden, experts, ids, wts, iters: int):
+    """Device time of each kernel stage of the prefill route of one layer (route, gather + quantize, FC1 with the
+    SwiGLU epilogue, FC2, combine), each captured into a CUDA graph of its own and replayed. A stage timed alone
+    runs at a higher clock than inside the power-capped layer, so the stages need not add up to the layer."""
+    t, h = int(hidden.shape[0]), int(hidden.shape[1])
+    e, inter, k = experts.num_experts, experts.inter, int(ids.shape[1])
+    plan = _ops.moe_plan(t, k, e)
+    rows = int(plan.rows)
+    _mm, blk0, slot, blk_expert = _ops.moe_route(ids, e, plan)
+    fp8 = torch.float8_e4m3fn
+    hq = torch.empty((rows, h), dtype=torch.uint8, device="cuda").view(fp8)
+    sh = torch.empty((rows * h // 128,), dtype=torch.int32, device="cuda")
+    dq = torch.empty((rows, inter), dtype=torch.uint8, device="cuda").view(fp8)
+    sd = torch.empty((rows * inter // 128,), dtype=torch.int32, device="cuda")
+    dn = torch.empty((rows, h), dtype=torch.bfloat16, device="cuda")
+    out = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    calls = {
+        "route_us": lambda i: _ops.moe_route(ids, e, plan),
+        "gather_quantize_us": lambda i: _ops.moe_gather_quant(hidden, slot, k, hq, sh),
+        "fc1_swiglu_us": lambda i: _ops.moe_fc1_swiglu(hq, sh, experts.w13, experts.sw13, blk0, blk_expert, dq, sd),
+        "fc2_us": lambda i: _ops.moe_fc2(dq, sd, experts.w2, experts.sw2, blk0, blk_expert, dn),
+        "combine_us": lambda i: _ops.moe_combine(dn, slot, wts, None, None, out),
+    }
+    res = {name: graph_replay_us(torch, fn, 1, iters) for name, fn in calls.items()}
+    res["blocks_in_use"] = int(blk0[-1].item())
+    res["note"] = "prefill route, one stage per CUDA graph; 128-row blocks in use include each expert's padding"
+    return res
 
 
 # ====================================================================================================== decode / quantize
@@ -870,6 +906,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize", "requant", "sweep"])
     ap.add_argument("--skew", type=float, default=0.0, help="moe workload: Zipf exponent of the expert popularity")
+    ap.add_argument("--stages", action="store_true",
+                    help="moe workload, one GPU: add the device time of each kernel stage of the layer")
     ap.add_argument("--no-sustained", action="store_true", help="dense workload: skip the two-second sustained run")
     ap.add_argument("--no-extras", action="store_true",
                     help="dense workload at one GPU: do not attach the decode / quantize / requant / Mixtral objects")
