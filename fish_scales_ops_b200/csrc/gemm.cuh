@@ -259,6 +259,26 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         mbar_fence_init();
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
+        if constexpr (kSwap && !kGrouped) {
+            // Decode-sized dense call: the weight side (MMA-M operand and its scales) of the first tile's first stages
+            // goes out here, before the CTA's set-up barrier and the tensor-memory allocation (which may have to wait
+            // for a predecessor's CTA on the same SM under programmatic dependent launch). Weights are immutable, so
+            // this needs no wait for the preceding kernel; the activation side follows in the producer after its wait.
+            TileCoord c0;
+            if (decode_tile<false, EPI == EPI_CLUSTER>(p, blockIdx.x, p.tiles_a, c0)) {
+                int const kb0 = c0.split * p.kb_per_split;
+                int const kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                int const a_row0 = c0.a_tile * C::kBM;
+                int const npre = min(S, kb1 - kb0);
+                for (int i = 0; i < npre; ++i) {
+                    uint32_t const fb = full_bar(i);
+                    mbar_expect_tx(fb, C::kABytes + C::kBBytes + C::kSfaBytes + 512u);
+                    tma_load_2d(sA + i * C::kABytes, &tm_a, fb, (kb0 + i) * C::kBK, a_row0);
+                    bulk_load(sSfa + i * C::kSfaBytes,
+                        p.sfa + (static_cast<int64_t>(a_row0 / 128) * p.kb_total + kb0 + i) * 512, 512, fb);
+                }
+            }
+        }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
@@ -314,18 +334,11 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t const bytes = C::kABytes + C::kBBytes + C::kSfaBytes + 512u * sfb_atoms;
                 if constexpr (kSwap && !kGrouped) {
                     if (first_tile) {
-                        // The weight side (MMA-M operand and its scales) of the first stages goes out before the
-                        // wait for the preceding kernel; the activation side, which that kernel may still be
-                        // writing, after it. All stages are free at this point, no empty-barrier wait is needed.
+                        // The weight side of the first stages went out during the CTA's set-up (above); the
+                        // activation side, which the preceding kernel may still be writing, follows its completion.
+                        // All stages are free at this point, no empty-barrier wait is needed.
                         first_tile = false;
                         int const npre = min(S, kb1 - kb0);
-                        for (int i = 0; i < npre; ++i) {
-                            uint32_t const fb = full_bar(i);
-                            mbar_expect_tx(fb, bytes);
-                            tma_load_2d(sA + i * C::kABytes, &tm_a, fb, (kb0 + i) * C::kBK, a_row0);
-                            bulk_load(sSfa + i * C::kSfaBytes,
-                                p.sfa + (static_cast<int64_t>(a_row0 / 128) * p.kb_total + kb0 + i) * 512, 512, fb);
-                        }
                         griddep_wait();
                         for (int i = 0; i < npre; ++i) {
                             uint32_t const fb = full_bar(i);
