@@ -20,6 +20,10 @@ Workloads (``--workload``):
             (cold weights). Metric: achieved weight-stream GB/s (worst of the four shapes).
   quantize  the activation quantizer alone on [8192, 4096]. Metric: GB/s.
   requant   the block-FP8 -> MXFP8 requantization kernel of prepare_weight alone on [24576, 7168]. Metric: GB/s.
+  bsfp8     BASELINE.json configs[2]: prepare_weight(format="bsfp8") on the three DeepSeek-V3 dense shapes and the
+            linears at M in {16, 512, 4096} on the prepared weights (CUDA-graph replay).
+  sweep     BASELINE.json configs[1] as one table: the four Llama-3-8B shapes x M in {1, 16, 128, 1024, 8192} with
+            cuBLAS' MXFP8 GEMM and a bf16 matmul in the same run.
 
 ``--impl reference`` times the reference's CPU statement of the same workload (the fp32 dequantize-then-matmul
 oracle under ``oracle/``, the only thing that runs there) on this box's host cores, on a bounded sample, and prints
@@ -898,13 +902,78 @@ def requant_ours(args):
     return line
 
 
+BSFP8_SHAPES = {"kv_b-like 7168x2048": (7168, 2048), "o-like 2048x7168": (2048, 7168), "wide 24576x7168": (24576, 7168)}
+
+
+def bsfp8_ours(args):
+    """BASELINE.json configs[2]: DeepSeek-V3 dense shapes stored as block-FP8 (one fp32 scale per 128 x 128 tile) are
+    requantized to MXFP8 at load (``prepare_weight(format="bsfp8")``: the requantization kernel + the end-of-prepare
+    fence) and then serve linears at M in {16, 512, 4096}. Per shape: the prepare time (eager calls, CUDA events) and
+    its GB/s (1 byte read + 1 + 1/32 written per element), and per M the linear (activation quantizer + GEMM) under
+    CUDA-graph replay."""
+    import torch
+
+    import fish_scales_ops_b200 as fso
+    from fish_scales_ops_b200 import _ops
+
+    d = shared_dist(torch)
+    fso.build()
+    pk = peaks()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    cells = {}
+    worst = None
+    with ClockSampler(d.local) as sampler:
+        for name, (n, k) in BSFP8_SHAPES.items():
+            wq = torch.randn(n, k, generator=g, device="cuda", dtype=torch.bfloat16).clamp_(-448, 448).to(
+                torch.float8_e4m3fn)
+            sc = torch.exp2(-8.0 + 4.0 * torch.rand(n // 128, k // 128, generator=g, device="cuda"))
+            for _ in range(3):
+                fso.dense.prepare_weight(wq, format="bsfp8", scale=sc)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                fso.dense.prepare_weight(wq, format="bsfp8", scale=sc)
+            e1.record()
+            torch.cuda.synchronize()
+            prep_us = e0.elapsed_time(e1) / 10 * 1e3            # eager calls: a load-time operation
+            weight = fso.dense.prepare_weight(wq, format="bsfp8", scale=sc)
+            nbytes = n * k * (2 + 1 / 32) + 4 * (n // 128) * (k // 128)
+            cell = {"N": n, "K": k, "prepare_us": prep_us, "prepare_gbs": nbytes / prep_us / 1e3,
+                    "prepare_frac_of_measured_hbm": nbytes / prep_us / 1e3 / pk["hbm_gbs"], "linear": {}}
+            for m in (16, 512, 4096):
+                x = torch.randn(m, k, generator=g, device="cuda", dtype=torch.bfloat16)
+                us = graph_replay_us(torch, lambda i: fso.dense.linear(x, weight), 1, 20)
+                cell["linear"][f"M={m}"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6,
+                                            "weight_stream_gbs": n * k * (1 + 1 / 32) / us / 1e3}
+            cells[name] = cell
+            worst = cell["prepare_gbs"]                    # the last (largest) shape: the one that streams from HBM
+            del wq, sc, weight
+            torch.cuda.empty_cache()
+    line = base_line(args, d, "bsfp8_prepare_gbs", "GB/s", worst, max(c["prepare_us"] for c in cells.values()) / 1e3,
+                     "strong", "fp8_e4m3 x f32 -> fp8_e4m3",
+                     {"workload": "block-FP8 checkpoints (128x128 fp32 scales) requantized to MXFP8 at load, then "
+                                  "linears at M in {16, 512, 4096}; value = the prepare of the 24576x7168 shape (the 15 MB shapes "
+                                  "are bound by the eager call itself, about 50 us)",
+                      "cells": cells, "l2": "the 7168x2048 / 2048x7168 weights (15 MB) fit in L2 under replay; the "
+                                            "24576x7168 one (176 MB) does not"})
+    line["roofline"] = {"bound": "hbm", "kernel": "requant_bs128_wide_kernel", "achieved": worst, "peak": pk["hbm_gbs"],
+                        "unit": "GB/s", "frac": worst / pk["hbm_gbs"], "traffic": None,
+                        "peak_source": f"{pk['source']} copy bandwidth"}
+    line["gpu_launches"] = 3 * (2 * 13 + 3 * 2 * 20)
+    line["clocks"] = sampler.summary()
+    line["device_status"] = _ops.device_status()
+    d.close()
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize", "requant", "sweep"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize", "requant", "sweep", "bsfp8"])
     ap.add_argument("--skew", type=float, default=0.0, help="moe workload: Zipf exponent of the expert popularity")
     ap.add_argument("--stages", action="store_true",
                     help="moe workload, one GPU: add the device time of each kernel stage of the layer")
@@ -930,7 +999,7 @@ def main():
 
             shared_dist(torch).keep = True
         line = {"dense": dense_ours, "moe": moe_ours, "decode": decode_ours, "quantize": quantize_ours,
-                "requant": requant_ours, "sweep": sweep_ours}[args.workload](args)
+                "requant": requant_ours, "sweep": sweep_ours, "bsfp8": bsfp8_ours}[args.workload](args)
         if both:
             # BASELINE.json's metric has two halves: the GEMM (the line itself) and the MoE layer's tokens/s at
             # 1/2/4/8 GPUs, which rides along as the line's "moe" object (same timing rules, fewer steps)
@@ -950,7 +1019,8 @@ def main():
                 ex = argparse.Namespace(**vars(args))
                 ex.steps, ex.warmup, ex.no_cpu_baseline, ex.no_parity = 20, 3, True, True
                 short = ("metric", "value", "unit", "ms_per_step", "config", "roofline", "clocks", "device_status")
-                for name, fn in (("decode", decode_ours), ("quantize", quantize_ours), ("requant", requant_ours)):
+                for name, fn in (("decode", decode_ours), ("quantize", quantize_ours), ("requant", requant_ours),
+                                 ("bsfp8", bsfp8_ours)):
                     sub_line = fn(ex)
                     line[name] = {k: sub_line[k] for k in short if k in sub_line}
                 torch.cuda.empty_cache()

@@ -10,6 +10,7 @@ from . import _ops
 from ._arch import SERVED_MAJOR, arch_label, device_arch
 
 __all__ = ["moe_topk_from_logits", "moe_router_topk", "silu_chunk_mul_quantize_1x32_fp8", "prepare_gate_up",
+           "shared_expert", "moe_layer_shared",
            "linear_swiglu"]
 
 _MAX_EXPERTS = 1024
@@ -212,3 +213,69 @@ def linear_swiglu(x: torch.Tensor, gate_up, *, x_scale: Optional[torch.Tensor] =
     k = gate_up.in_features
     x2 = x if x_scale is not None else x.reshape(-1, k)
     return torch.ops.fish_scales_ops.dense_linear_swiglu(x2, gate_up.weight, gate_up.scale, x_scale)
+
+
+# ------------------------------------------------------------------------------------------- shared expert overlap
+
+# One side stream per process for the shared expert, created on first use: creating a stream inside a CUDA-graph
+# capture would put host-side set-up in the middle of the capture (python/fish_scales_ops/gemm/mxfp8.py:2389-2408).
+_SIDE_STREAM = None
+
+
+def _side_stream():
+    global _SIDE_STREAM
+    if _SIDE_STREAM is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("fso.compat.moe_layer_shared: the first overlapped call of a process creates the side "
+                               "stream of the shared expert, which cannot happen inside a CUDA-graph capture; call it "
+                               "once eagerly before capturing, or pass overlap=False (FSO_MOE_BLOCK_OVERLAP=0 turns "
+                               "the overlap off process-wide)")
+        _SIDE_STREAM = torch.cuda.Stream()
+    return _SIDE_STREAM
+
+
+def _overlap_default() -> bool:
+    import os
+
+    return os.environ.get("FSO_MOE_BLOCK_OVERLAP", "1").strip().lower() not in ("0", "false", "off", "no")
+
+
+def shared_expert(hidden: torch.Tensor, gate_up, down) -> torch.Tensor:
+    """The always-on dense expert of a MoE block: ``(silu(x W_gate^T) * (x W_up^T)) W_down^T`` as two GEMM launches
+    and the activation quantizer (gate_up with the fused SiLU(gate)*up requantizing epilogue, then down); bf16
+    ``[M, H]``. ``gate_up`` from :func:`prepare_gate_up`, ``down`` from ``fso.dense.prepare_weight``
+    (python/fish_scales_ops/gemm/mxfp8.py:2421-2428 runs the same chain in four kernels)."""
+    from . import dense
+
+    hq, hs = linear_swiglu(hidden, gate_up)
+    return dense.linear(hq, down, x_scale=hs)
+
+
+def moe_layer_shared(hidden: torch.Tensor, experts, topk_ids: torch.Tensor, topk_w: torch.Tensor, *, gate_up, down,
+                     shared_gate: Optional[torch.Tensor] = None, overlap: Optional[bool] = None) -> torch.Tensor:
+    """The routed experts of ``fso.moe.layer`` plus a shared expert, added inside the combine kernel:
+    ``out[t] = sum_j topk_w[t, j] * expert_{ids[t, j]}(hidden[t]) + shared_gate[t] * shared(hidden[t])``.
+
+    With ``overlap`` (default on; ``FSO_MOE_BLOCK_OVERLAP=0`` turns it off process-wide) the shared expert depends
+    only on the layer's input, so it is issued on a side stream and waited for at the latest point that needs it:
+    right before the combine. The two branches run concurrently, eagerly and inside a captured graph alike; the
+    output is bit-identical either way, the join being a stream dependency and not a change of arithmetic
+    (python/fish_scales_ops/gemm/mxfp8.py:2578-2611)."""
+    from . import moe
+
+    use_overlap = _overlap_default() if overlap is None else bool(overlap)
+    if not use_overlap or hidden.shape[0] == 0:
+        bias = shared_expert(hidden, gate_up, down)
+        return moe.layer(hidden, experts, topk_ids, topk_w, bias=bias, bias_scale=shared_gate)
+    current = torch.cuda.current_stream()
+    side = _side_stream()
+    side.wait_stream(current)
+    with torch.cuda.stream(side):
+        bias = shared_expert(hidden, gate_up, down)
+    # the combine reads it on the current stream: the allocator must not hand the block out again before that read
+    bias.record_stream(current)
+    moe._BEFORE_COMBINE.fn = lambda: current.wait_stream(side)
+    try:
+        return moe.layer(hidden, experts, topk_ids, topk_w, bias=bias, bias_scale=shared_gate)
+    finally:
+        moe._BEFORE_COMBINE.fn = None

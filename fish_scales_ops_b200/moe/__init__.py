@@ -12,6 +12,8 @@ to -1 and reduces the partial sums itself.
 """
 import dataclasses
 
+import threading
+
 import torch
 
 from .. import _ops
@@ -308,6 +310,11 @@ def _require_experts_aligned(w13, sw13, w2, sw2, where: str) -> None:
             raise ValueError(f"fish_scales_ops::moe_layer ({where}, kind 'mxfp8'): {name} must be contiguous")
 
 
+# A stream dependency to establish right before the combine kernel of the next layer call of this thread (set by
+# fso.compat.moe_layer_shared, whose shared expert runs on a side stream and is only read by the combine).
+_BEFORE_COMBINE = threading.local()
+
+
 def _run_layer(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale):
     t, h = int(hidden.shape[0]), int(hidden.shape[1])
     e, two_i, _ = (int(v) for v in w13.shape)
@@ -338,6 +345,9 @@ def _run_layer(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale):
             _ops.moe_grouped_gemm_decode(dq, sd, w2, sw2, masked_m, blk0, blk_expert, dn, t, topk)
         else:
             _ops.moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn)
+        join = getattr(_BEFORE_COMBINE, "fn", None)
+        if join is not None:
+            join()
         _ops.moe_combine(dn, slot, topk_w, bias, bias_scale, out)
     return out
 

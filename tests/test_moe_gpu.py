@@ -325,3 +325,48 @@ def test_decode_band_graph_replay_with_rewritten_routing(fso, device_ok, monkeyp
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, fso.moe.layer(hidden, ex, ids, wts))
+
+
+# ------------------------------------------------------------------------------------------ shared expert overlap
+
+def _shared_weights(fso, h, inter, seed):
+    from fish_scales_ops_b200 import compat
+
+    g = torch.Generator().manual_seed(seed)
+    w_gu = (0.02 * torch.randn(2 * inter, h, generator=g)).to(torch.bfloat16)
+    w_dn = (0.02 * torch.randn(h, inter, generator=g)).to(torch.bfloat16)
+    return compat.prepare_gate_up(w_gu.cuda()), fso.dense.prepare_weight(w_dn.cuda(), format="mxfp8")
+
+
+@pytest.mark.parametrize("t", [5, 200])
+def test_shared_expert_joined_before_the_combine(fso, device_ok, t):
+    """The shared expert on a side stream, joined right before the combine that adds it: the bytes of the sequential
+    form and of fso.moe.layer fed the same bias (python/fish_scales_ops/gemm/mxfp8.py:2578-2611: the join is a stream
+    dependency, not a change of arithmetic). Covers the decode band (5 tokens) and the prefill route."""
+    from fish_scales_ops_b200 import compat
+
+    e, h, i, k = 8, 256, 256, 2
+    _, _, ex = _prepare(fso, e, h, i, 31)
+    gate_up, down = _shared_weights(fso, h, 384, 32)
+    hidden = inputs.activation(t, h, 33).cuda()
+    ids, wts = inputs.routing(t, e, k, 34)
+    ids, wts = ids.cuda(), wts.cuda()
+    gate = torch.sigmoid(torch.randn(t, generator=torch.Generator().manual_seed(35))).cuda()
+    bias = compat.shared_expert(hidden, gate_up, down)
+    want = fso.moe.layer(hidden, ex, ids, wts, bias=bias, bias_scale=gate)
+    seq = compat.moe_layer_shared(hidden, ex, ids, wts, gate_up=gate_up, down=down, shared_gate=gate, overlap=False)
+    ovl = compat.moe_layer_shared(hidden, ex, ids, wts, gate_up=gate_up, down=down, shared_gate=gate, overlap=True)
+    torch.cuda.synchronize()
+    assert torch.equal(seq, want) and torch.equal(ovl, want)
+    # and inside a captured graph (the side stream exists by now): two branches, joined before the combine
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            out = compat.moe_layer_shared(hidden, ex, ids, wts, gate_up=gate_up, down=down, shared_gate=gate)
+    torch.cuda.current_stream().wait_stream(stream)
+    out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
