@@ -179,6 +179,29 @@ inline int pdl_attribute(cudaLaunchAttribute* attr)
     return 1;
 }
 
+// FSO_PRINT_TILE_INFO=1: print, once per kernel instantiation that is launched, the tile it runs, the stage count
+// its shared-memory budget gave and the resources it asks for (host side, read once, off unless set; the reference's
+// switch of the same name, arch/sm100/mxfp8/grouped_dispatch.cuh:162-176).
+inline bool print_tile_info()
+{
+    static int const v = [] {
+        const char* e = std::getenv("FSO_PRINT_TILE_INFO");
+        return (e != nullptr && e[0] != '\0' && e[0] != '0') ? 1 : 0;
+    }();
+    return v != 0;
+}
+
+inline void print_tile_info_once(std::atomic<int>& printed, const char* kernel, int bm, int bn, int epi, bool swap,
+    bool grouped, bool fused, int stages, int smem_bytes, int threads, int tmem_cols)
+{
+    if (!print_tile_info() || printed.exchange(1) != 0) return;
+    std::fprintf(stderr,
+        "[fso_b200] %s: tile %d x %d x 128, epilogue %d, %s orientation%s%s, %d stages, %d bytes of shared memory, "
+        "%d threads, %d tensor-memory columns\n",
+        kernel, bm, bn, epi, swap ? "swapped" : "normal", grouped ? ", grouped" : "", fused ? ", fused epilogue" : "",
+        stages, smem_bytes, threads, tmem_cols);
+}
+
 template <int BN, int EPI, bool kSwap, bool kGrouped, bool kFused = false>
 inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmParams const& p, int grid,
     cudaStream_t stream)
@@ -188,6 +211,9 @@ inline int launch_gemm_inst(CUtensorMap const& ta, CUtensorMap const& tb, GemmPa
     auto kernel = gemm_mxf8_kernel<BN, EPI, kSwap, kGrouped, kFused>;
     int const rc = ensure_smem_attr(kernel, C::kSmemBytes, done);
     if (rc != 0) return rc;
+    static std::atomic<int> printed{0};
+    print_tile_info_once(printed, "gemm_mxf8_kernel", C::kBM, BN, EPI, kSwap, kGrouped, kFused, C::kStages, C::kSmemBytes,
+        C::kThreads, C::kTmemCols);
     if constexpr (kSwap) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
@@ -271,6 +297,10 @@ inline int launch_gemm_cluster(CUtensorMap const& ta, CUtensorMap const& tb, Gem
         int const rc = ensure_smem_attr(kernel, GemmCfg<BN, EPI_CLUSTER>::kSmemBytes, done);
         if (rc != 0) return rc;
     }
+    using C = GemmCfg<BN, EPI_CLUSTER>;
+    static std::atomic<int> printed{0};
+    print_tile_info_once(printed, "gemm_mxf8_kernel (split-K inside clusters)", C::kBM, BN, EPI_CLUSTER, true, kGrouped,
+        kFused, C::kStages, C::kSmemBytes, C::kThreads, C::kTmemCols);
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     cluster_launch_config<BN>(cfg, attr, items, p.splits, stream);
@@ -352,6 +382,9 @@ inline int launch_dense_pair(const void* a, const void* sfa, const void* w, cons
     static std::atomic<uint64_t> done{0};
     rc = ensure_smem_attr(gemm_mxf8_pair_kernel, Gemm2Cfg::kSmemBytes, done);
     if (rc != 0) return rc;
+    static std::atomic<int> printed{0};
+    print_tile_info_once(printed, "gemm_mxf8_pair_kernel (per CTA of the pair)", Gemm2Cfg::kBM, Gemm2Cfg::kBN, EPI_BF16,
+        false, false, false, Gemm2Cfg::kStages, Gemm2Cfg::kSmemBytes, Gemm2Cfg::kThreads, Gemm2Cfg::kTmemCols);
     gemm_mxf8_pair_kernel<<<2 * pairs, Gemm2Cfg::kThreads, Gemm2Cfg::kSmemBytes, stream>>>(ta, tb, tsa, tsb, p);
     return launch_status("gemm_mxf8_pair_kernel");
 }

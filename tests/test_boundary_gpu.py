@@ -203,3 +203,89 @@ def test_bounded_wait_sets_the_status_word(fso):
     weight = fso.dense.prepare_weight(inputs.weight(256, 512, 1).cuda(), format="mxfp8")
     y = fso.dense.linear(inputs.activation(16, 512, 2).cuda(), weight)
     assert torch.isfinite(y.float()).all() and _ops.device_status() == 0
+
+
+def test_outputs_stay_inside_their_buffers(fso, device_ok):
+    """Guard bands: every output of the C-ABI calls below sits inside a larger buffer filled with a canary byte; after
+    the call the bytes before and after the output still hold the canary. Shapes with ragged last tiles (rows past M
+    in the last 128-row tile, the second CTA of a CTA pair without rows, a decode-sized call, the quantizing and the
+    SwiGLU epilogue)."""
+    from fish_scales_ops_b200 import _ops
+    from fish_scales_ops_b200._ops import check, lib, ptr, sf_words, stream_ptr
+
+    guard = 4096
+    canary = 0xA5
+
+    def banded(nbytes):
+        buf = torch.full((guard + nbytes + guard,), canary, dtype=torch.uint8, device="cuda")
+        return buf, buf[guard:guard + nbytes]
+
+    def intact(buf, nbytes, what):
+        torch.cuda.synchronize()
+        assert bool((buf[:guard] == canary).all()) and bool((buf[guard + nbytes:] == canary).all()), what
+
+    g = torch.Generator(device="cuda").manual_seed(77)
+    for m, n, k in ((200, 512, 256), (1920, 5120, 256), (2100, 4096, 512), (5, 4096, 1024), (16, 512, 4096)):
+        x = torch.randn(m, k, generator=g, device="cuda", dtype=torch.bfloat16)
+        w = (0.02 * torch.randn(n, k, generator=g, device="cuda")).to(torch.bfloat16)
+        weight = fso.dense.prepare_weight(w, format="mxfp8")
+        # activation quantizer: codes and scale words
+        qbuf, q = banded(m * k)
+        sbuf, s = banded(4 * sf_words(m, k))
+        check(lib().fso_quantize_activation_1x32(ptr(x), ptr(q), ptr(s), m, k, stream_ptr()), "quantize")
+        intact(qbuf, m * k, f"quantizer codes {m}x{k}")
+        intact(sbuf, 4 * sf_words(m, k), f"quantizer scale words {m}x{k}")
+        xq, sx = q.view(torch.float8_e4m3fn).view(m, k), s.view(torch.int32)
+        # GEMM, bf16 output
+        ws_bytes = _ops.gemm_ws_bytes(m, n, k)
+        ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device="cuda")
+        ybuf, y = banded(2 * m * n)
+        check(lib().fso_gemm_mxfp8(ptr(xq), ptr(sx), ptr(weight.weight), ptr(weight.scale), ptr(y), m, n, k, ptr(ws),
+                                   ws_bytes, stream_ptr()), "gemm")
+        intact(ybuf, 2 * m * n, f"bf16 output {m}x{n}x{k}")
+        assert torch.equal(y.view(torch.bfloat16).view(m, n), fso.dense.linear(x, weight))
+        # GEMM with the quantizing epilogue, where the shape takes it
+        if _ops.gemm_fuses_quantized_output(m, n, k):
+            obuf, o = banded(m * n)
+            fbuf, f = banded(4 * sf_words(m, n))
+            check(lib().fso_gemm_mxfp8_quantized(ptr(xq), ptr(sx), ptr(weight.weight), ptr(weight.scale), ptr(o), ptr(f),
+                                                 m, n, k, None, 0, stream_ptr()), "gemm quantized")
+            intact(obuf, m * n, f"quantized output {m}x{n}x{k}")
+            intact(fbuf, 4 * sf_words(m, n), f"quantized output scale words {m}x{n}x{k}")
+        # gate_up with the SwiGLU epilogue (normal orientation at every M)
+        if n % 256 == 0:
+            obuf, o = banded(m * (n // 2))
+            fbuf, f = banded(4 * sf_words(m, n // 2))
+            check(lib().fso_gemm_mxfp8_swiglu(ptr(xq), ptr(sx), ptr(weight.weight), ptr(weight.scale), ptr(o), ptr(f), m,
+                                              n, k, stream_ptr()), "gemm swiglu")
+            intact(obuf, m * (n // 2), f"SwiGLU output {m}x{n}x{k}")
+            intact(fbuf, 4 * sf_words(m, n // 2), f"SwiGLU output scale words {m}x{n}x{k}")
+    assert _ops.device_status() == 0
+
+
+def test_print_tile_info_switch(device_ok):
+    """FSO_PRINT_TILE_INFO=1 prints, once per kernel instantiation that is launched, the tile and the resources it
+    asks for; nothing is printed without the variable (read once per process: child processes)."""
+    import os
+    import subprocess
+    import sys
+
+    code = ("import torch, fish_scales_ops_b200 as fso\n"
+            "w = fso.dense.prepare_weight(torch.randn(512, 256, device='cuda').to(torch.bfloat16), format='mxfp8')\n"
+            "x = torch.randn(256, 256, device='cuda').to(torch.bfloat16)\n"
+            "for _ in range(3): fso.dense.linear(x, w)\n"
+            "fso.dense.linear(x[:8], w)\n"
+            "torch.cuda.synchronize()\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for flag, expect in (("1", True), (None, False)):
+        env = {k: v for k, v in os.environ.items() if k != "FSO_PRINT_TILE_INFO"}
+        if flag is not None:
+            env["FSO_PRINT_TILE_INFO"] = flag
+        res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stderr[-2000:]
+        lines = [ln for ln in res.stderr.splitlines() if ln.startswith("[fso_b200] gemm_mxf8")]
+        if expect:
+            assert len(lines) == 2 and len(set(lines)) == 2, lines     # one per instantiation, not one per call
+            assert "normal orientation" in lines[0] and "swapped orientation" in lines[1], lines
+        else:
+            assert not lines, lines
