@@ -105,7 +105,18 @@ def ptr(t):
 
 
 def stream_ptr():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device as a raw handle (no Stream object is built: this sits on the path of
+    every call)."""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
+
+
+def eager_or_op(body, op, *args):
+    """An eager call runs the op's body directly (the dispatcher round trip of a Python custom op costs more host time
+    than a decode-sized kernel runs); while torch.compile traces, the registered custom op is called instead, so the
+    compiled graph records it as one node."""
+    if torch.compiler.is_compiling():
+        return op(*args)
+    return body(*args)
 
 
 def device_status() -> int:

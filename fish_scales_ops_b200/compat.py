@@ -7,6 +7,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _ops
+from ._lib import eager_or_op
 from ._arch import SERVED_MAJOR, arch_label, device_arch
 
 __all__ = ["moe_topk_from_logits", "moe_router_topk", "silu_chunk_mul_quantize_1x32_fp8", "prepare_gate_up",
@@ -17,13 +18,7 @@ _MAX_EXPERTS = 1024
 _MAX_TOPK = 8
 
 
-@torch.library.custom_op(
-    "fish_scales_ops::moe_topk_from_logits",
-    mutates_args=(),
-    schema="(Tensor logits, int topk, bool renormalize=True, bool with_shared_gate=False, "
-           "Tensor? num_token_non_padded=None, Tensor? expert_map=None) -> (Tensor, Tensor, Tensor)",
-)
-def _topk_from_logits_op(logits, topk, renormalize=True, with_shared_gate=False, num_token_non_padded=None,
+def _topk_from_logits_body(logits, topk, renormalize=True, with_shared_gate=False, num_token_non_padded=None,
                          expert_map=None):
     """Body of ``torch.ops.fish_scales_ops.moe_topk_from_logits`` (csrc/gemm/ops/moe_glue.cu:3074-3152): the same
     refusals, before anything is launched."""
@@ -57,6 +52,14 @@ def _topk_from_logits_op(logits, topk, renormalize=True, with_shared_gate=False,
     return _ops.moe_topk_from_logits(logits, int(topk), bool(renormalize), bool(with_shared_gate), n_valid, emap)
 
 
+_topk_from_logits_op = torch.library.custom_op(
+    "fish_scales_ops::moe_topk_from_logits",
+    mutates_args=(),
+    schema="(Tensor logits, int topk, bool renormalize=True, bool with_shared_gate=False, "
+           "Tensor? num_token_non_padded=None, Tensor? expert_map=None) -> (Tensor, Tensor, Tensor)",
+)(_topk_from_logits_body)
+
+
 @_topk_from_logits_op.register_fake
 def _topk_from_logits_fake(logits, topk, renormalize=True, with_shared_gate=False, num_token_non_padded=None,
                            expert_map=None):
@@ -74,8 +77,8 @@ def moe_topk_from_logits(logits: torch.Tensor, topk: int, *, renormalize: bool =
     probabilities by their own sum, otherwise the weights are the plain softmax over all experts; rows at or past
     ``num_token_non_padded`` get the sentinel id ``num_experts`` (through ``expert_map`` when given) and weight
     zero; ``expert_map`` int32 ``[num_experts + 1]`` maps global ids to an expert-parallel rank's local ids."""
-    return torch.ops.fish_scales_ops.moe_topk_from_logits(logits, int(topk), bool(renormalize), bool(with_shared_gate),
-                                                          num_token_non_padded, expert_map)
+    return eager_or_op(_topk_from_logits_body, torch.ops.fish_scales_ops.moe_topk_from_logits, logits, int(topk),
+                       bool(renormalize), bool(with_shared_gate), num_token_non_padded, expert_map)
 
 
 def moe_router_topk(hidden: torch.Tensor, router_weight: torch.Tensor, topk: int, *, renormalize: bool = True,
@@ -88,12 +91,7 @@ def moe_router_topk(hidden: torch.Tensor, router_weight: torch.Tensor, topk: int
                                 num_token_non_padded=num_token_non_padded, expert_map=expert_map)
 
 
-@torch.library.custom_op(
-    "fish_scales_ops::silu_chunk_mul_quantize_1x32",
-    mutates_args=(),
-    schema="(Tensor gu, bool use_ue8m0=True) -> (Tensor, Tensor)",
-)
-def _silu_chunk_mul_quantize_op(gu, use_ue8m0=True):
+def _silu_chunk_mul_quantize_body(gu, use_ue8m0=True):
     op = f"fish_scales_ops::silu_chunk_mul_quantize_1x32 ({arch_label(device_arch())})"
     if not gu.is_cuda or gu.dtype != torch.bfloat16 or gu.dim() != 2:
         raise ValueError(f"{op}: gu must be a CUDA bf16 [M, 2*INTER] tensor, got {gu.dtype} {tuple(gu.shape)}")
@@ -106,6 +104,13 @@ def _silu_chunk_mul_quantize_op(gu, use_ue8m0=True):
     if not gu.is_contiguous() or gu.data_ptr() % 32 != 0:
         gu = gu.contiguous() if not gu.is_contiguous() else gu.clone()
     return _ops.silu_mul_quantize_1x32_fp8(gu)
+
+
+_silu_chunk_mul_quantize_op = torch.library.custom_op(
+    "fish_scales_ops::silu_chunk_mul_quantize_1x32",
+    mutates_args=(),
+    schema="(Tensor gu, bool use_ue8m0=True) -> (Tensor, Tensor)",
+)(_silu_chunk_mul_quantize_body)
 
 
 @_silu_chunk_mul_quantize_op.register_fake
@@ -122,7 +127,8 @@ def silu_chunk_mul_quantize_1x32_fp8(gu: torch.Tensor) -> Tuple[torch.Tensor, to
     the activation contract, ready for ``fso.dense.linear(xq, weight, x_scale=sx)``, without the product ever
     reaching memory."""
     two_i = int(gu.shape[-1])
-    return torch.ops.fish_scales_ops.silu_chunk_mul_quantize_1x32(gu.reshape(-1, two_i), True)
+    return eager_or_op(_silu_chunk_mul_quantize_body, torch.ops.fish_scales_ops.silu_chunk_mul_quantize_1x32,
+                       gu.reshape(-1, two_i), True)
 
 
 # ------------------------------------------------------------------------------------------ dense SwiGLU, fused
@@ -161,12 +167,7 @@ def prepare_gate_up(w: torch.Tensor, *, format: str = "mxfp8", scale: Optional[t
     return dense.DenseWeight("mxfp8", format, arch, k, two_i, q, sq)
 
 
-@torch.library.custom_op(
-    "fish_scales_ops::dense_linear_swiglu",
-    mutates_args=(),
-    schema="(Tensor x, Tensor weight, Tensor scale, Tensor? x_scale=None) -> (Tensor, Tensor)",
-)
-def _dense_linear_swiglu_op(x, weight, scale, x_scale=None):
+def _dense_linear_swiglu_body(x, weight, scale, x_scale=None):
     op = f"fish_scales_ops::dense_linear_swiglu ({arch_label(device_arch())})"
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise ValueError(f"{op}: x must be [M, K] and weight [2*INTER, K] with the same K, got {tuple(x.shape)} and "
@@ -191,6 +192,13 @@ def _dense_linear_swiglu_op(x, weight, scale, x_scale=None):
     return _ops.linear_mxfp8_swiglu(x, weight, x_scale, scale)
 
 
+_dense_linear_swiglu_op = torch.library.custom_op(
+    "fish_scales_ops::dense_linear_swiglu",
+    mutates_args=(),
+    schema="(Tensor x, Tensor weight, Tensor scale, Tensor? x_scale=None) -> (Tensor, Tensor)",
+)(_dense_linear_swiglu_body)
+
+
 @_dense_linear_swiglu_op.register_fake
 def _dense_linear_swiglu_fake(x, weight, scale, x_scale=None):
     m, inter = x.shape[0], weight.shape[0] // 2
@@ -212,7 +220,8 @@ def linear_swiglu(x: torch.Tensor, gate_up, *, x_scale: Optional[torch.Tensor] =
                         f"{type(gate_up).__name__}")
     k = gate_up.in_features
     x2 = x if x_scale is not None else x.reshape(-1, k)
-    return torch.ops.fish_scales_ops.dense_linear_swiglu(x2, gate_up.weight, gate_up.scale, x_scale)
+    return eager_or_op(_dense_linear_swiglu_body, torch.ops.fish_scales_ops.dense_linear_swiglu, x2, gate_up.weight,
+                       gate_up.scale, x_scale)
 
 
 # ------------------------------------------------------------------------------------------- shared expert overlap

@@ -19,6 +19,7 @@ import os
 import torch
 
 from .. import _ops
+from .._lib import eager_or_op
 from .._arch import SERVED_MAJOR, arch_label, arch_major, device_arch, sm_major
 
 __all__ = ["FORMATS", "ACTIVATIONS", "DenseWeight", "prepare_weight", "linear", "linear_quantized",
@@ -383,13 +384,7 @@ def _epilogue_storage(op: str, bias, residual):
 
 # ------------------------------------------------------------------------------------------------ custom ops
 
-@torch.library.custom_op(
-    "fish_scales_ops::dense_linear",
-    mutates_args=(),
-    schema="(Tensor x, Tensor weight, Tensor scale, str kind, Tensor? bias=None, Tensor? x_scale=None, "
-           "Tensor? residual=None, str? activation=None) -> Tensor",
-)
-def _dense_linear_op(x, weight, scale, kind, bias=None, x_scale=None, residual=None, activation=None):
+def _dense_linear_body(x, weight, scale, kind, bias=None, x_scale=None, residual=None, activation=None):
     """Body of ``torch.ops.fish_scales_ops.dense_linear``: metadata checks only (no sync, no dependence on tensor
     values), then the quantizer and the GEMM (python/fish_scales_ops/dense/__init__.py:962-993)."""
     op = f"fish_scales_ops::dense_linear ({arch_label(device_arch())}, kind {kind!r})"
@@ -412,6 +407,14 @@ def _dense_linear_op(x, weight, scale, kind, bias=None, x_scale=None, residual=N
     return _ops.linear_mxfp8(x, weight, x_scale, scale, bias, residual, 1 if activation == "gelu_erf" else 0)
 
 
+_dense_linear_op = torch.library.custom_op(
+    "fish_scales_ops::dense_linear",
+    mutates_args=(),
+    schema="(Tensor x, Tensor weight, Tensor scale, str kind, Tensor? bias=None, Tensor? x_scale=None, "
+           "Tensor? residual=None, str? activation=None) -> Tensor",
+)(_dense_linear_body)
+
+
 @_dense_linear_op.register_fake
 def _dense_linear_fake(x, weight, scale, kind, bias=None, x_scale=None, residual=None, activation=None):
     if x.dim() != 2 or weight.dim() != 2:
@@ -420,13 +423,7 @@ def _dense_linear_fake(x, weight, scale, kind, bias=None, x_scale=None, residual
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op(
-    "fish_scales_ops::dense_linear_quantized",
-    mutates_args=(),
-    schema="(Tensor x, Tensor weight, Tensor scale, str kind, Tensor? bias=None, Tensor? x_scale=None, "
-           "str? activation=None) -> (Tensor, Tensor)",
-)
-def _dense_linear_quantized_op(x, weight, scale, kind, bias=None, x_scale=None, activation=None):
+def _dense_linear_quantized_body(x, weight, scale, kind, bias=None, x_scale=None, activation=None):
     """Body of ``torch.ops.fish_scales_ops.dense_linear_quantized``: the result of ``dense_linear`` in the
     activation contract (python/fish_scales_ops/dense/__init__.py:1212-1241). For the shapes the GEMM serves in its
     normal orientation without split-K the quantization happens in the GEMM's epilogue (one launch, no bf16 round
@@ -449,6 +446,14 @@ def _dense_linear_quantized_op(x, weight, scale, kind, bias=None, x_scale=None, 
     if x_scale is None:
         x, x_scale = _ops.quantize_1x32_fp8(x, activation=True)
     return _ops.linear_mxfp8_quantized(x, weight, x_scale, scale, bias, 1 if activation == "gelu_erf" else 0)
+
+
+_dense_linear_quantized_op = torch.library.custom_op(
+    "fish_scales_ops::dense_linear_quantized",
+    mutates_args=(),
+    schema="(Tensor x, Tensor weight, Tensor scale, str kind, Tensor? bias=None, Tensor? x_scale=None, "
+           "str? activation=None) -> (Tensor, Tensor)",
+)(_dense_linear_quantized_body)
 
 
 @_dense_linear_quantized_op.register_fake
@@ -475,12 +480,7 @@ def _quantize_activation_checks(x, op: str) -> None:
         raise ValueError(f"{op}: activation contract v1 needs K to be a multiple of 128 and K is {k}")
 
 
-@torch.library.custom_op(
-    "fish_scales_ops::dense_quantize_activation",
-    mutates_args=(),
-    schema="(Tensor x) -> (Tensor, Tensor)",
-)
-def _dense_quantize_activation_op(x):
+def _dense_quantize_activation_body(x):
     op = f"fish_scales_ops::dense_quantize_activation ({arch_label(device_arch())})"
     _quantize_activation_checks(x, op)
     k = int(x.shape[-1])
@@ -489,6 +489,13 @@ def _dense_quantize_activation_op(x):
     if m == 0:
         return (x.new_empty((0, k), dtype=FP8), _empty_act_scale(0, k, x.device))
     return _ops.quantize_1x32_fp8(x2, activation=True)
+
+
+_dense_quantize_activation_op = torch.library.custom_op(
+    "fish_scales_ops::dense_quantize_activation",
+    mutates_args=(),
+    schema="(Tensor x) -> (Tensor, Tensor)",
+)(_dense_quantize_activation_body)
 
 
 @_dense_quantize_activation_op.register_fake
@@ -562,7 +569,8 @@ def linear(x, weight, *, bias=None, x_scale=None, residual=None, activation=None
             raise ValueError(f"fso.dense.linear ({where}, kind {weight.kind!r}): the residual must be contiguous")
         res2 = residual.view(-1, n)
     extra = _trim_none(bias, x_scale, res2, activation)
-    y = torch.ops.fish_scales_ops.dense_linear(x2, weight.weight, weight.scale, weight.kind, *extra)
+    y = eager_or_op(_dense_linear_body, torch.ops.fish_scales_ops.dense_linear, x2, weight.weight, weight.scale,
+                    weight.kind, *extra)
     return y.reshape(out_shape)
 
 
@@ -572,11 +580,12 @@ def linear_quantized(x, weight, *, bias=None, x_scale=None, activation=None):
     where = arch_label(device_arch())
     _check_handle(weight, where, "fso.dense.linear_quantized")
     x2, _ = _flatten_x(x, weight, x_scale, where, "fso.dense.linear_quantized")
-    return torch.ops.fish_scales_ops.dense_linear_quantized(
+    return eager_or_op(_dense_linear_quantized_body, torch.ops.fish_scales_ops.dense_linear_quantized,
+        
         x2, weight.weight, weight.scale, weight.kind, *_trim_none(bias, x_scale, activation))
 
 
 def quantize_activation(x):
     """``(xq, x_scale)`` of a bf16 ``[..., K]`` activation: float8_e4m3fn ``[M, K]`` and the int32 atom-layout
     scale words, the exact bytes ``linear(x, weight)`` computes inside the op."""
-    return torch.ops.fish_scales_ops.dense_quantize_activation(x)
+    return eager_or_op(_dense_quantize_activation_body, torch.ops.fish_scales_ops.dense_quantize_activation, x)

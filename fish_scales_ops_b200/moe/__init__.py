@@ -17,6 +17,7 @@ import threading
 import torch
 
 from .. import _ops
+from .._lib import eager_or_op
 from .._arch import SERVED_MAJOR, arch_label, arch_major, device_arch, sm_major
 
 __all__ = ["FORMATS", "MoeExperts", "prepare_experts", "layer", "transient_bytes", "supported", "describe"]
@@ -384,13 +385,7 @@ def _run_layer_rows(rx_q, rx_w, experts, topk_ids, topk_w, recv_off, back_base, 
         _ops.moe_combine_scatter(dn, slot, topk_w, recv_off, back_base, peer_back, world)
 
 
-@torch.library.custom_op(
-    "fish_scales_ops::moe_layer",
-    mutates_args=(),
-    schema="(Tensor hidden, Tensor w13, Tensor sw13, Tensor w2, Tensor sw2, Tensor topk_ids, "
-           "Tensor topk_w, Tensor? bias, Tensor? bias_scale, str kind, bool w13_interleaved) -> Tensor",
-)
-def _moe_layer_op(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale, kind, w13_interleaved):
+def _moe_layer_body(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale, kind, w13_interleaved):
     """Body of ``torch.ops.fish_scales_ops.moe_layer`` (python/fish_scales_ops/moe/__init__.py:651-719)."""
     arch = device_arch()
     where = arch_label(arch)
@@ -422,6 +417,14 @@ def _moe_layer_op(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale
     if int(hidden.shape[0]) == 0:
         return hidden.new_empty(hidden.shape)
     return _run_layer(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale)
+
+
+_moe_layer_op = torch.library.custom_op(
+    "fish_scales_ops::moe_layer",
+    mutates_args=(),
+    schema="(Tensor hidden, Tensor w13, Tensor sw13, Tensor w2, Tensor sw2, Tensor topk_ids, "
+           "Tensor topk_w, Tensor? bias, Tensor? bias_scale, str kind, bool w13_interleaved) -> Tensor",
+)(_moe_layer_body)
 
 
 @_moe_layer_op.register_fake
@@ -466,9 +469,9 @@ def layer(hidden, experts, topk_ids, topk_w, *, bias=None, bias_scale=None) -> t
         bias_scale = bias_scale.reshape(m).to(torch.float32).contiguous()
     ids = topk_ids.to(torch.int32).contiguous()
     wts = topk_w.to(torch.float32).contiguous()
-    return torch.ops.fish_scales_ops.moe_layer(hidden.contiguous(), experts.w13, experts.sw13, experts.w2, experts.sw2,
-                                               ids, wts, None if bias is None else bias.contiguous(), bias_scale,
-                                               experts.kind, experts.w13_interleaved)
+    return eager_or_op(_moe_layer_body, torch.ops.fish_scales_ops.moe_layer, hidden.contiguous(), experts.w13,
+                       experts.sw13, experts.w2, experts.sw2, ids, wts, None if bias is None else bias.contiguous(),
+                       bias_scale, experts.kind, experts.w13_interleaved)
 
 
 def transient_bytes(experts, tokens, topk) -> int:
