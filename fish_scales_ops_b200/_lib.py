@@ -104,6 +104,26 @@ def ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def on_device(device):
+    """Context in which ``device`` is the current CUDA device: nothing at all when it already is (the usual case, and
+    this sits on the path of every call), ``torch.cuda.device`` otherwise."""
+    idx = device.index if isinstance(device, torch.device) else device
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(idx)
+
+
 def stream_ptr():
     """The current stream of the current device as a raw handle (no Stream object is built: this sits on the path of
     every call)."""

@@ -11,7 +11,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import MoePlan, check, lib, ptr, stream_ptr
+from ._lib import MoePlan, check, lib, on_device, ptr, stream_ptr
 
 FP8 = torch.float8_e4m3fn
 
@@ -34,7 +34,7 @@ def quantize_1x32_fp8(x: torch.Tensor, interleave_i: int = 0, activation: bool =
     m, k = int(x.shape[0]), int(x.shape[1])
     if k % 128 != 0:
         raise ValueError(f"quantize_1x32_fp8: K = {k} is not a multiple of 128")
-    with torch.cuda.device(x.device):
+    with on_device(x.device):
         xq = torch.empty((m, k), dtype=FP8, device=x.device)
         sf = torch.empty((sf_words(m, k),), dtype=torch.int32, device=x.device)
         if m > 0 and activation and interleave_i == 0:
@@ -50,7 +50,7 @@ def silu_mul_quantize_1x32_fp8(gu: torch.Tensor):
     """bf16 [M, 2I] (gate | up) -> (float8_e4m3fn [M, I], int32 scale words): silu(gate) * up, quantized."""
     m, two_i = int(gu.shape[0]), int(gu.shape[1])
     inter = two_i // 2
-    with torch.cuda.device(gu.device):
+    with on_device(gu.device):
         xq = torch.empty((m, inter), dtype=FP8, device=gu.device)
         sf = torch.empty((sf_words(m, inter),), dtype=torch.int32, device=gu.device)
         if m > 0:
@@ -61,7 +61,7 @@ def silu_mul_quantize_1x32_fp8(gu: torch.Tensor):
 
 def stream_fence(device) -> None:
     """One empty plain launch on the current stream of ``device`` (orders programmatic dependent launches)."""
-    with torch.cuda.device(device):
+    with on_device(device):
         check(lib().fso_stream_fence(stream_ptr()), "fso_stream_fence")
 
 
@@ -82,7 +82,7 @@ def requant_block_fp8(wq: torch.Tensor, scale: torch.Tensor, interleave_i: int =
     n, k = int(wq.shape[0]), int(wq.shape[1])
     wq = wq.contiguous()
     scale = scale.contiguous()
-    with torch.cuda.device(wq.device):
+    with on_device(wq.device):
         q = torch.empty((n, k), dtype=FP8, device=wq.device)
         sf = torch.empty((sf_words(n, k),), dtype=torch.int32, device=wq.device)
         check(lib().fso_requant_bs128_to_mx(ptr(wq), ptr(scale), ptr(q), ptr(sf), n, k, int(interleave_i), stream_ptr()),
@@ -97,7 +97,7 @@ def pack_ue8m0(sf_u8: torch.Tensor, interleave: bool = False) -> torch.Tensor:
                          f"{list(sf_u8.shape)}")
     s = sf_u8.contiguous()
     g, n, k = int(s.shape[0]), int(s.shape[1]), int(s.shape[2]) * 32
-    with torch.cuda.device(s.device):
+    with on_device(s.device):
         out = torch.empty((g, sf_words(n, k)), dtype=torch.int32, device=s.device)
         check(lib().fso_pack_ue8m0(ptr(s), ptr(out), g, n, k, n // 2 if interleave else 0, stream_ptr()),
               "fso_pack_ue8m0")
@@ -116,7 +116,7 @@ def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.
     the dense epilogue bf16(act(acc + bias) + residual) when any of its fields is given."""
     m, k = int(xq.shape[0]), int(xq.shape[1])
     n = int(w.shape[0])
-    with torch.cuda.device(xq.device):
+    with on_device(xq.device):
         out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
         if m == 0:
             return out
@@ -151,7 +151,7 @@ def linear_mxfp8_quantized(xq, w, sx, sw, bias=None, activation: int = 0):
     where the shape allows, otherwise the GEMM followed by the activation quantizer."""
     m, k = int(xq.shape[0]), int(xq.shape[1])
     n = int(w.shape[0])
-    with torch.cuda.device(xq.device):
+    with on_device(xq.device):
         if m > 0 and gemm_fuses_quantized_output(m, n, k):
             out = torch.empty((m, n), dtype=FP8, device=xq.device)
             sf = torch.empty((sf_words(m, n),), dtype=torch.int32, device=xq.device)
@@ -168,7 +168,7 @@ def linear_mxfp8_swiglu(xq, w_interleaved, sx, sw):
     m, k = int(xq.shape[0]), int(xq.shape[1])
     two_i = int(w_interleaved.shape[0])
     inter = two_i // 2
-    with torch.cuda.device(xq.device):
+    with on_device(xq.device):
         dq = torch.empty((m, inter), dtype=FP8, device=xq.device)
         sd = torch.empty((sf_words(m, inter),), dtype=torch.int32, device=xq.device)
         if m > 0:
@@ -187,7 +187,7 @@ def moe_route(ids: torch.Tensor, num_experts: int, plan: MoePlan):
     """ids int32 [T, topk] -> (masked_m [E], blk0 [E+1], slot_of_flat [T*topk], blk_expert [num_blocks])."""
     t, topk = int(ids.shape[0]), int(ids.shape[1])
     dev = ids.device
-    with torch.cuda.device(dev):
+    with on_device(dev):
         masked_m = torch.empty((num_experts,), dtype=torch.int32, device=dev)
         blk0 = torch.empty((num_experts + 1,), dtype=torch.int32, device=dev)
         slot = torch.empty((t * topk,), dtype=torch.int32, device=dev)
@@ -201,14 +201,14 @@ def moe_route(ids: torch.Tensor, num_experts: int, plan: MoePlan):
 
 def moe_gather_quant(hidden: torch.Tensor, slot: torch.Tensor, topk: int, hq: torch.Tensor, sh: torch.Tensor):
     t, h = int(hidden.shape[0]), int(hidden.shape[1])
-    with torch.cuda.device(hidden.device):
+    with on_device(hidden.device):
         check(lib().fso_moe_gather_quant(ptr(hidden), ptr(slot), t, topk, h, int(hq.shape[0]), ptr(hq), ptr(sh),
                                          stream_ptr()), "fso_moe_gather_quant")
 
 
 def moe_fc1_swiglu(hq, sh, w13, sw13, blk0, blk_expert, dq, sd):
     e, two_i, h = (int(v) for v in w13.shape)
-    with torch.cuda.device(hq.device):
+    with on_device(hq.device):
         check(lib().fso_moe_fc1_swiglu(ptr(hq), ptr(sh), ptr(w13), ptr(sw13), ptr(blk0), ptr(blk_expert), e, h,
                                        two_i // 2, int(blk_expert.shape[0]), int(hq.shape[0]), ptr(dq), ptr(sd),
                                        stream_ptr()), "fso_moe_fc1_swiglu")
@@ -216,7 +216,7 @@ def moe_fc1_swiglu(hq, sh, w13, sw13, blk0, blk_expert, dq, sd):
 
 def moe_fc2(dq, sd, w2, sw2, blk0, blk_expert, dn):
     e, h, inter = (int(v) for v in w2.shape)
-    with torch.cuda.device(dq.device):
+    with on_device(dq.device):
         check(lib().fso_moe_fc2(ptr(dq), ptr(sd), ptr(w2), ptr(sw2), ptr(blk0), ptr(blk_expert), e, h, inter,
                                 int(blk_expert.shape[0]), int(dq.shape[0]), ptr(dn), stream_ptr()), "fso_moe_fc2")
 
@@ -225,7 +225,7 @@ def moe_grouped_gemm_decode(act_q, act_sf, weight, sfw, masked_m, blk0, blk_expe
     """out [rows, n_w] (fp32 or bf16, by its dtype) = the routed rows of act_q [rows, K] times weight [E, n_w, K]^T
     per expert, decode band."""
     e, n_w, k = (int(v) for v in weight.shape)
-    with torch.cuda.device(act_q.device):
+    with on_device(act_q.device):
         check(lib().fso_moe_grouped_gemm_decode(ptr(act_q), ptr(act_sf), ptr(weight), ptr(sfw), ptr(masked_m), ptr(blk0),
                                                 ptr(blk_expert), e, n_w, k, int(blk_expert.shape[0]),
                                                 int(act_q.shape[0]), ptr(out), 1 if out.dtype == torch.float32 else 0,
@@ -235,7 +235,7 @@ def moe_grouped_gemm_decode(act_q, act_sf, weight, sfw, masked_m, blk0, blk_expe
 
 def moe_silu_mul_quantize_rows(gu, masked_m, blk0, blk_expert, num_experts: int, dq, sd):
     rows, inter = int(dq.shape[0]), int(dq.shape[1])
-    with torch.cuda.device(gu.device):
+    with on_device(gu.device):
         check(lib().fso_moe_silu_mul_quantize_rows(ptr(gu), ptr(masked_m), ptr(blk0), ptr(blk_expert), int(num_experts),
                                                    rows, inter, ptr(dq), ptr(sd), stream_ptr()),
               "fso_moe_silu_mul_quantize_rows")
@@ -244,7 +244,7 @@ def moe_silu_mul_quantize_rows(gu, masked_m, blk0, blk_expert, num_experts: int,
 def moe_combine(dn, slot, topk_w, bias, bias_scale, out):
     t, h = int(out.shape[0]), int(out.shape[1])
     topk = int(topk_w.shape[1])
-    with torch.cuda.device(dn.device):
+    with on_device(dn.device):
         check(lib().fso_moe_combine(ptr(dn), ptr(slot), ptr(topk_w), ptr(bias), ptr(bias_scale), ptr(out), t, topk, h,
                                     stream_ptr()), "fso_moe_combine")
 
@@ -257,7 +257,7 @@ def moe_topk_from_logits(logits, topk: int, renormalize: bool, with_shared_gate:
     m, width = int(logits.shape[0]), int(logits.shape[1])
     e = width - (1 if with_shared_gate else 0)
     dev = logits.device
-    with torch.cuda.device(dev):
+    with on_device(dev):
         ids = torch.empty((m, topk), dtype=torch.int32, device=dev)
         w = torch.empty((m, topk), dtype=torch.float32, device=dev)
         gate = torch.empty((m if with_shared_gate else 0,), dtype=torch.float32, device=dev)
@@ -272,7 +272,7 @@ def ep_plan_count(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
     """int32 [T, k] global ids -> (rank_mask int64 [T], row int64 [world + 1] = rows per destination rank, T)."""
     t, k = int(topk_ids.shape[0]), int(topk_ids.shape[1])
     dev = topk_ids.device
-    with torch.cuda.device(dev):
+    with on_device(dev):
         mask = torch.empty((t,), dtype=torch.int64, device=dev)
         row = torch.empty((world + 1,), dtype=torch.int64, device=dev)
         check(lib().fso_ep_plan_count(ptr(topk_ids), t, k, int(experts_per_rank), int(world), ptr(mask), ptr(row),
@@ -283,7 +283,7 @@ def ep_plan_count(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
 def ep_plan_place(mask: torch.Tensor, table: torch.Tensor, world: int, rank: int, send_total: int):
     """-> (send_token [S], send_rank [S], send_off [G], dst_base [G], recv_off [G + 1], back_base [G], slot [T, G])."""
     t, dev = int(mask.shape[0]), mask.device
-    with torch.cuda.device(dev):
+    with on_device(dev):
         lists = torch.empty((2, max(send_total, 1)), dtype=torch.int64, device=dev)
         offs = torch.empty((4 * world + 1,), dtype=torch.int64, device=dev)
         slot = torch.empty((t, world), dtype=torch.int32, device=dev)
@@ -299,7 +299,7 @@ def ep_dispatch_push(xq, xs, topk_ids, topk_w, send_token, send_rank, send_off, 
                      peer_wt, experts_per_rank: int):
     """Store this rank's sent rows into the destination ranks' receive buffers (peer-mapped addresses)."""
     rows, topk, h = int(send_token.shape[0]), int(topk_ids.shape[1]), int(xq.shape[1])
-    with torch.cuda.device(xq.device):
+    with on_device(xq.device):
         check(lib().fso_ep_dispatch_push(ptr(xq), ptr(xs), ptr(topk_ids), ptr(topk_w), ptr(send_token), ptr(send_rank),
                                          ptr(send_off), ptr(dst_base), ptr(peer_q), ptr(peer_w), ptr(peer_ids),
                                          ptr(peer_wt), rows, topk, h, int(experts_per_rank), stream_ptr()),
@@ -308,14 +308,14 @@ def ep_dispatch_push(xq, xs, topk_ids, topk_w, send_token, send_rank, send_off, 
 
 def moe_gather_rows(rx_q, rx_w, slot, topk: int, hq, sh):
     rows_in, h = int(rx_q.shape[0]), int(rx_q.shape[1])
-    with torch.cuda.device(rx_q.device):
+    with on_device(rx_q.device):
         check(lib().fso_moe_gather_rows(ptr(rx_q), ptr(rx_w), ptr(slot), rows_in, topk, h, int(hq.shape[0]), ptr(hq),
                                         ptr(sh), stream_ptr()), "fso_moe_gather_rows")
 
 
 def moe_combine_scatter(dn, slot, topk_w, recv_off, back_base, peer_back, world: int):
     tokens, topk, h = int(topk_w.shape[0]), int(topk_w.shape[1]), int(dn.shape[1])
-    with torch.cuda.device(dn.device):
+    with on_device(dn.device):
         check(lib().fso_moe_combine_scatter(ptr(dn), ptr(slot), ptr(topk_w), tokens, topk, h, ptr(recv_off),
                                             ptr(back_base), ptr(peer_back), int(world), stream_ptr()),
               "fso_moe_combine_scatter")

@@ -17,7 +17,7 @@ import threading
 import torch
 
 from .. import _ops
-from .._lib import eager_or_op
+from .._lib import eager_or_op, on_device
 from .._arch import SERVED_MAJOR, arch_label, arch_major, device_arch, sm_major
 
 __all__ = ["FORMATS", "MoeExperts", "prepare_experts", "layer", "transient_bytes", "supported", "describe"]
@@ -323,7 +323,7 @@ def _run_layer(hidden, w13, sw13, w2, sw2, topk_ids, topk_w, bias, bias_scale):
     topk = int(topk_ids.shape[1])
     dev = hidden.device
     plan = _layer_plan(t, topk, e, h, inter)
-    with torch.cuda.device(dev):
+    with on_device(dev):
         mplan = _ops.moe_plan(t, topk, e)
         masked_m, blk0, slot, blk_expert = _ops.moe_route(topk_ids, e, mplan)
         region = torch.empty((plan.region,), dtype=torch.uint8, device=dev)
@@ -370,7 +370,7 @@ def _run_layer_rows(rx_q, rx_w, experts, topk_ids, topk_w, recv_off, back_base, 
     dev = rx_q.device
     _require_experts_aligned(w13, sw13, w2, sw2, "expert-parallel")
     plan = _layer_plan(r, topk, e, h, inter)
-    with torch.cuda.device(dev):
+    with on_device(dev):
         mplan = _ops.moe_plan(r, topk, e)
         masked_m, blk0, slot, blk_expert = _ops.moe_route(topk_ids, e, mplan)
         region = torch.empty((plan.region,), dtype=torch.uint8, device=dev)
