@@ -41,7 +41,7 @@ struct GemmParams {
     const int32_t* blk0;       // grouped: blk0[num_experts] = blocks in use
     const int32_t* blk_expert; // grouped: expert of each 128-row block
     const int32_t* masked_m;   // grouped + swapped: routed rows of each expert
-    int subs;                  // grouped + swapped: token sub-tiles per 128-row block (128 / BN)
+    int subs;                  // grouped + swapped: token sub-tiles per 128-row block (128 / BN, fewer for a handful of pairs)
     int out_f32;               // grouped + swapped: `out` is fp32 [rows, ldo] (the accumulators, not rounded)
     int rows_a;                // valid rows of the MMA-M operand
     int rows_b;                // valid rows of the MMA-N operand (per expert when grouped)

@@ -650,7 +650,10 @@ inline int launch_grouped_swap(const void* a, const void* sfa, const void* weigh
     p.kb_total = static_cast<int>(k / 128);
     p.tiles_a = static_cast<int>(n_w / 128);
     p.tiles_b = static_cast<int>(num_blocks);
-    p.subs = 128 / bn;
+    // token sub-tiles of a 128-row block that can hold rows at all: an expert has at most `pairs` rows, so with a
+    // handful of tokens only the first sub-tile exists and the tile space (the grid of the one-shot form) shrinks
+    int64_t const subs_needed = ((pairs < 128 ? pairs : 128) + bn - 1) / bn;
+    p.subs = static_cast<int>(subs_needed < 1 ? 1 : subs_needed);
     p.ldo = static_cast<int>(n_w);
     p.num_experts = static_cast<int>(num_experts);
     p.group_a = 1;

@@ -29,10 +29,11 @@ FP8 = torch.float8_e4m3fn
 _REGION_ALIGN = 1024
 # The decode band (the reference's slot route, python/fish_scales_ops/gemm/mxfp8.py:540-551: "expected rows per expert
 # <= 64"): calls of at most 64 tokens whose routed pairs are at most twice the experts they can reach, so that an
-# expert in use holds a row or two. There the swapped grouped GEMM (weights on MMA-M, only the experts in use) beats
-# the 128-row tiles of the prefill kernels: measured under CUDA-graph replay, Mixtral 1 token 111 -> 84 us, 4 tokens
-# 136 -> 121 us, DeepSeek-V3 16 tokens 841 -> 772 us, 64 tokens 1674 -> 1575 us (0.98 of the live weights' stream);
-# with more rows per expert (Mixtral 16 / 64 tokens) the prefill kernels stream the weights faster and keep the call.
+# expert in use holds a row or two, or at most 32 pairs, so that a block has one 32-row token sub-tile. There the
+# swapped grouped GEMM (weights on MMA-M, only the experts in use) beats the 128-row tiles of the prefill kernels:
+# measured under CUDA-graph replay, Mixtral 1 token 108 -> 81 us, 4 tokens 132 -> 114 us, 16 tokens 261 -> 242 us,
+# DeepSeek-V3 16 tokens 841 -> 772 us, 64 tokens 1674 -> 1575 us (0.98 of the live weights' stream); with more rows
+# per expert (Mixtral 24 to 64 tokens) the prefill kernels stream the weights faster and keep the call.
 # FC2 takes the band whenever the call is in it; FC1 only when its live tiles fill the half-SM CTA slots one and a
 # half times over (otherwise the fused prefill FC1, with its 256-row weight tiles, is ahead: DeepSeek-V3 1 token).
 # Both choices are functions of (tokens, top-k, E, I, SM count) alone, so a captured graph replays for any routing.
@@ -56,7 +57,8 @@ def _decode_band(tokens: int, topk: int, num_experts: int, inter: int):
         return True, True
     pairs = tokens * topk
     live = min(pairs, num_experts)
-    if pairs > 2 * live:
+    # at most two rows per expert in use, or so few pairs that every block has a single 32-row token sub-tile
+    if pairs > 2 * live and pairs > 32:
         return False, False
     return live * (2 * inter // 128) >= 3 * _sm_count(), True
 
