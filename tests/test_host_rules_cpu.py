@@ -1,0 +1,73 @@
+"""Host-side rules that need no GPU: the decode-band rule of the MoE layer (a pure function of the call's shape and
+the SM count) and the eager / traced dispatch of the public calls."""
+import pytest
+import torch
+
+
+@pytest.fixture()
+def moe_mod(monkeypatch):
+    from fish_scales_ops_b200 import moe
+
+    monkeypatch.setattr(moe, "_sm_count", lambda: 148)
+    monkeypatch.delenv("FSO_B200_MOE_DECODE", raising=False)
+    return moe
+
+
+# (tokens, top-k, experts, I) -> (FC1 takes the band, FC2 takes the band)
+BAND_CASES = [
+    ((1, 2, 8, 14336), (True, True)),       # Mixtral, one token: two experts in use, 448 FC1 tiles
+    ((4, 2, 8, 14336), (True, True)),
+    ((16, 2, 8, 14336), (True, True)),      # 32 pairs: one 32-row token sub-tile per block
+    ((24, 2, 8, 14336), (False, False)),    # six rows per expert: the prefill kernels keep the call
+    ((64, 2, 8, 14336), (False, False)),
+    ((64, 8, 256, 2048), (True, True)),     # DeepSeek-V3: two rows per expert in use
+    ((1, 8, 256, 2048), (False, True)),     # eight experts x 32 FC1 panels do not fill the half-SM slots 1.5 times
+    ((65, 8, 256, 2048), (False, False)),   # past the band's token limit
+    ((0, 2, 8, 14336), (False, False)),
+]
+
+
+@pytest.mark.parametrize("shape,want", BAND_CASES)
+def test_decode_band_rule(moe_mod, shape, want):
+    assert moe_mod._decode_band(*shape) == want
+
+
+def test_decode_band_switches(moe_mod, monkeypatch):
+    monkeypatch.setenv("FSO_B200_MOE_DECODE", "0")
+    assert moe_mod._decode_band(1, 2, 8, 14336) == (False, False)
+    monkeypatch.setenv("FSO_B200_MOE_DECODE", "force")
+    assert moe_mod._decode_band(64, 2, 8, 14336) == (True, True)
+    assert moe_mod._decode_band(65, 2, 8, 14336) == (False, False)
+
+
+def test_eager_calls_run_the_body_and_traced_calls_the_op():
+    from fish_scales_ops_b200._lib import eager_or_op
+
+    calls = []
+    body = lambda *a: calls.append(("body", a)) or "body"      # noqa: E731
+    op = lambda *a: calls.append(("op", a)) or "op"            # noqa: E731
+    assert eager_or_op(body, op, 1, 2) == "body" and calls == [("body", (1, 2))]
+
+    @torch.library.custom_op("fso_test::twice", mutates_args=())
+    def twice(x: torch.Tensor) -> torch.Tensor:
+        return x * 2
+
+    @twice.register_fake
+    def _(x):
+        return torch.empty_like(x)
+
+    seen = []
+
+    def traced(x):
+        seen.append(torch.compiler.is_compiling())
+        return eager_or_op(lambda t: t * 2, torch.ops.fso_test.twice, x)
+
+    x = torch.arange(4.0)
+    assert torch.equal(traced(x), x * 2) and seen == [False]
+    from torch._dynamo.testing import EagerAndRecordGraphs
+
+    backend = EagerAndRecordGraphs()
+    out = torch.compile(traced, backend=backend, fullgraph=True)(x)
+    assert torch.equal(out, x * 2)
+    nodes = [n for g in backend.graphs for n in g.graph.nodes if n.op == "call_function"]
+    assert len(nodes) == 1 and "fso_test" in str(nodes[0].target)
