@@ -152,10 +152,11 @@ def test_refusals_before_launch(fso, device_ok):
 def test_cuda_graph_capture_and_no_sync(fso, oracle, device_ok):
     """Capture after one eager call, NaN-filled replay buffers, replay == eager after rewriting x in place; the call
     never synchronizes (python side of tests/gemm/unit/test_cuda_graph.py:33-80 of the reference)."""
-    for m in (16, 384):
-        w = inputs.weight(512, 1024, 21)
+    # a decode-sized call, a single-CTA-kernel call and one the CTA-pair kernel takes (128 tiles of 256 x 256)
+    for m, n, k in ((16, 512, 1024), (384, 512, 1024), (2048, 4096, 512)):
+        w = inputs.weight(n, k, 21)
         weight = fso.dense.prepare_weight(w.cuda(), format="mxfp8")
-        x = inputs.activation(m, 1024, 22).cuda()
+        x = inputs.activation(m, k, 22).cuda()
         eager = fso.dense.linear(x, weight)
         torch.cuda.synchronize()
         torch.cuda.set_sync_debug_mode("error")
@@ -176,7 +177,7 @@ def test_cuda_graph_capture_and_no_sync(fso, oracle, device_ok):
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, eager)
-        x2 = inputs.activation(m, 1024, 23).cuda()
+        x2 = inputs.activation(m, k, 23).cuda()
         static_x.copy_(x2)
         graph.replay()
         torch.cuda.synchronize()
