@@ -587,6 +587,20 @@ def moe_ours(args):
     stages = None
     if d.world == 1 and getattr(args, "stages", False):
         stages = moe_stage_times(torch, _ops, hidden, experts, ids, wts, max(5, min(args.steps, 20)))
+    elif d.world > 1 and getattr(args, "stages", False) and ep_transport_is_peer():
+        # phases of the expert-parallel step on this rank (CUDA events between the phases of the peer transport; the
+        # host read shows up as the idle time its synchronisation leaves on the stream)
+        sums, reps = {}, max(5, min(args.steps, 20))
+        for _ in range(reps):
+            parallel.PHASE_TRACE = []
+            run(hidden)
+            torch.cuda.synchronize()
+            marks = parallel.PHASE_TRACE
+            parallel.PHASE_TRACE = None
+            for (_, ev_a), (name, ev_b) in zip(marks[:-1], marks[1:]):
+                sums[name] = sums.get(name, 0.0) + ev_a.elapsed_time(ev_b)
+        stages = {f"{name} (ms)": v / reps for name, v in sums.items()}
+        stages["note"] = f"rank {d.rank}, {reps} steps, device time between phase boundaries of the peer transport"
     ms_total, e2e_ms = d.max_over_ranks([ms_total, e2e_ms])
     status = _ops.device_status()
     # correctness of what was timed: rank 0's first tokens against the CPU oracle (every N), and under expert
@@ -668,6 +682,10 @@ def moe_ours(args):
                                 "frac_of_measured_hbm": live_bytes / (replay_us * 1e-6) / (pk["hbm_gbs"] * 1e9)}
     d.close()
     return line
+
+
+def ep_transport_is_peer() -> bool:
+    return os.environ.get("FSO_B200_EP_TRANSPORT", "") in ("", "peer")
 
 
 def moe_stage_times(torch, _ops, hidden, experts, ids, wts, iters: int):
@@ -976,7 +994,8 @@ def main():
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "decode", "quantize", "requant", "sweep", "bsfp8"])
     ap.add_argument("--skew", type=float, default=0.0, help="moe workload: Zipf exponent of the expert popularity")
     ap.add_argument("--stages", action="store_true",
-                    help="moe workload, one GPU: add the device time of each kernel stage of the layer")
+                    help="moe workload: add the device time of each kernel stage of the layer (one GPU) or of each phase "
+                         "of the expert-parallel step (several GPUs, rank 0)")
     ap.add_argument("--no-sustained", action="store_true", help="dense workload: skip the two-second sustained run")
     ap.add_argument("--no-extras", action="store_true",
                     help="dense workload at one GPU: do not attach the decode / quantize / requant / Mixtral objects")

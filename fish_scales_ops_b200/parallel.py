@@ -196,6 +196,18 @@ def _fence(bufs: _PeerBuffers, group) -> None:
     dist.all_reduce(bufs.fence_word, group=group)
 
 
+# Phase trace of the peer transport (measurement only): when this is a list, every phase boundary of
+# _expert_parallel_peer appends (name, CUDA event recorded on the current stream).
+PHASE_TRACE = None
+
+
+def _mark(name: str) -> None:
+    if PHASE_TRACE is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        PHASE_TRACE.append((name, ev))
+
+
 def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: int, group) -> torch.Tensor:
     """Expert parallelism with the rows stored straight into the destination GPU's memory.
 
@@ -213,19 +225,29 @@ def _expert_parallel_peer(hidden, experts, topk_ids, topk_w, per: int, world: in
 
     rank = dist.get_rank(group)
     t, h, k = int(hidden.shape[0]), int(hidden.shape[1]), int(topk_ids.shape[1])
+    _mark("start")
     ids32 = topk_ids.to(torch.int32).contiguous()
     w32 = topk_w.to(torch.float32).contiguous()
     mask, row = _ops.ep_plan_count(ids32, per, world)
     table = torch.empty((world, world + 1), dtype=torch.int64, device=hidden.device)
     dist.all_gather_into_tensor(table, row, group=group)
+    _mark("plan count + all-gather")
     quantized = _ops.quantize_1x32_fp8(hidden) if t > 0 else None            # runs while the host waits below
+    _mark("quantize")
     host = table.tolist()                                                     # the one host read
     bufs = _peer_buffers(group, world, max(r[world] for r in host), h, k, hidden.device)
+    _mark("host read")
     st = _peer_dispatch(hidden, ids32, w32, mask, table, host, rank, world, per, bufs, quantized)
+    _mark("plan place + dispatch")
     _fence(bufs, group)
+    _mark("fence")
     _peer_local(st, experts, bufs)
+    _mark("local layer incl. scatter combine")
     _fence(bufs, group)
-    return _peer_reduce(st, bufs)
+    _mark("fence 2")
+    out = _peer_reduce(st, bufs)
+    _mark("final reduce")
+    return out
 
 
 def _peer_dispatch(hidden, ids32, w32, mask, table, host, rank: int, world: int, per: int, bufs: _PeerBuffers,
