@@ -63,7 +63,33 @@ struct DensePlan {
     int tiles_a, tiles_b;
     int group_a;
     int64_t ws_bytes;
+    double cost;    // normal orientation: rounds of the persistent schedule x tile width (see plan_dense)
 };
+
+// FSO_B200_DENSE_TILE=256 | 128 | pair forces the tile of the normal-orientation calls where that tile can serve the
+// shape (measurement; read once per process). Unset: the picker below decides.
+inline int forced_dense_tile()
+{
+    static int const v = [] {
+        const char* e = std::getenv("FSO_B200_DENSE_TILE");
+        if (e == nullptr) return 0;
+        if (std::strcmp(e, "pair") == 0) return 2;
+        int const t = std::atoi(e);
+        return (t == 256 || t == 128) ? t : 0;
+    }();
+    return v;
+}
+
+// Rounds a persistent grid of `slots` CTAs (or CTA pairs) needs for `tiles` equal tiles.
+inline double schedule_rounds(int64_t tiles, int64_t slots)
+{
+    return static_cast<double>((tiles + slots - 1) / slots);
+}
+
+// A 128-wide tile moves twice the weight bytes per flop of a 256-wide one, so a round of 128-wide tiles is charged
+// more than half a round of 256-wide ones: 1.17-1.22 measured on five shapes with both tiles forced (1024 x 28672,
+// 4096 x 4096, 1024 x 6144, 2048 x 6144, 512 x 28672; K = 4096).
+constexpr double kNarrowTilePenalty = 1.18;
 
 // Fraction of the (persistent, one CTA per SM) grid kept busy by `items` equal work items.
 inline double wave_efficiency(int64_t items, int sms)
@@ -134,7 +160,15 @@ inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
     } else {
         p.swap = false;
         int const tiles_m = static_cast<int>((m + 127) / 128);
-        p.bn = (n % 256 == 0 && static_cast<int64_t>(tiles_m) * (n / 256) >= sms / 2) ? 256 : 128;
+        // Tile width by the rounds of the persistent schedule: a round costs its tile width (an MMA's time is
+        // proportional to N). Whole problems of at most half a round of 256-wide tiles and shapes that leave the last
+        // round of 256-wide tiles nearly empty (1024 x 6144: 192 tiles on 148 SMs) take 128-wide tiles.
+        double const c256 = n % 256 == 0 ? schedule_rounds(static_cast<int64_t>(tiles_m) * (n / 256), sms) * 256.0 : 1e30;
+        double const c128 = schedule_rounds(static_cast<int64_t>(tiles_m) * ((n + 127) / 128), sms) * 128.0
+            * kNarrowTilePenalty;
+        p.bn = c256 <= c128 ? 256 : 128;
+        if (forced_dense_tile() == 128 || (forced_dense_tile() == 256 && n % 256 == 0)) p.bn = forced_dense_tile();
+        p.cost = p.bn == 256 ? c256 : c128;
         p.tiles_a = tiles_m;
         p.tiles_b = static_cast<int>((n + p.bn - 1) / p.bn);
         p.group_a = tiles_m < 16 ? tiles_m : 16;
@@ -437,8 +471,13 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
             static_cast<long long>(k));
         return FSO_ERR_UNSUPPORTED;
     }
-    if (!fused && !quant && use_pair_kernel(m, n, sms, pl.swap, pl.splits))
-        return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
+    if (!fused && !quant && use_pair_kernel(m, n, sms, pl.swap, pl.splits)) {
+        // the pair kernel's rounds are 256 wide and about 4 % cheaper than the single-CTA kernel's
+        double const cpair = schedule_rounds(((m + 255) / 256) * (n / 256), sms / 2) * 256.0 * 0.96;
+        int const forced = forced_dense_tile();
+        if (forced == 2 || (forced == 0 && cpair <= pl.cost))
+            return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
+    }
     CUtensorMap ta, tb;
     GemmParams p{};
     p.kb_total = static_cast<int>(k / 128);
