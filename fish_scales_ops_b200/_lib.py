@@ -23,6 +23,7 @@ SIGNATURES = {
     "fso_requant_bs128_to_mx": [_c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p],
     "fso_pack_ue8m0": [_c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p],
     "fso_gemm_mxfp8_ws_bytes": [_c_i64, _c_i64, _c_i64, ctypes.POINTER(_c_i64)],
+    "fso_gemm_mxfp8_describe": [_c_i64, _c_i64, _c_i64, _c_i64, ctypes.POINTER(ctypes.c_int32)],
     "fso_gemm_mxfp8": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_i64, _c_i64, _c_p, _c_i64, _c_p],
     "fso_moe_plan_make": [_c_i64, _c_i64, _c_i64, _c_p],
     "fso_moe_route": [_c_p, _c_i64, _c_i64, _c_i64, _c_i64, _c_p, _c_p, _c_p, _c_p, _c_p, _c_i64, _c_p],

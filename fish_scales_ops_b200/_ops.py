@@ -110,6 +110,14 @@ def gemm_ws_bytes(m: int, n: int, k: int) -> int:
     return int(v.value)
 
 
+def gemm_describe(m: int, n: int, k: int, sm_count: int = 0) -> dict:
+    """The route the dense GEMM takes for one shape (host arithmetic only; ``sm_count`` 0 = the current device's)."""
+    out = (ctypes.c_int32 * 6)()
+    check(lib().fso_gemm_mxfp8_describe(m, n, k, sm_count, out), "fso_gemm_mxfp8_describe")
+    return {"swapped": bool(out[0]), "tile_n": int(out[1]), "k_slices": int(out[2]), "k_blocks_per_slice": int(out[3]),
+            "pair_kernel": bool(out[4]), "tiles": int(out[5])}
+
+
 def linear_mxfp8(xq: torch.Tensor, w: torch.Tensor, sx: torch.Tensor, sw: torch.Tensor, bias=None, residual=None,
                  activation: int = 0) -> torch.Tensor:
     """bf16 [M, N] = xq [M, K] @ w [N, K]^T over MXFP8 operands (python/fish_scales_ops/gemm/mxfp8.py:90-188), with

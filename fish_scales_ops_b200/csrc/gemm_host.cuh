@@ -388,6 +388,18 @@ inline bool use_pair_kernel(int64_t m, int64_t n, int sms, bool swap, int splits
     return tiles >= sms / 2;
 }
 
+// Whether a plain (no fused epilogue) dense call of this plan runs on the CTA-pair kernel: the shape must suit it and
+// its rounds (256 wide on SMs / 2 pairs, about 4 % cheaper than the single-CTA kernel's) must not cost more than the
+// plan's.
+inline bool dense_takes_pair(int64_t m, int64_t n, int sms, DensePlan const& pl)
+{
+    if (!use_pair_kernel(m, n, sms, pl.swap, pl.splits)) return false;
+    int const forced = forced_dense_tile();
+    if (forced != 0) return forced == 2;
+    double const cpair = schedule_rounds(((m + 255) / 256) * (n / 256), sms / 2) * 256.0 * 0.96;
+    return cpair <= pl.cost;
+}
+
 inline int launch_dense_pair(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m,
     int64_t n, int64_t k, int sms, cudaStream_t stream)
 {
@@ -471,13 +483,8 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
             static_cast<long long>(k));
         return FSO_ERR_UNSUPPORTED;
     }
-    if (!fused && !quant && use_pair_kernel(m, n, sms, pl.swap, pl.splits)) {
-        // the pair kernel's rounds are 256 wide and about 4 % cheaper than the single-CTA kernel's
-        double const cpair = schedule_rounds(((m + 255) / 256) * (n / 256), sms / 2) * 256.0 * 0.96;
-        int const forced = forced_dense_tile();
-        if (forced == 2 || (forced == 0 && cpair <= pl.cost))
-            return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
-    }
+    if (!fused && !quant && dense_takes_pair(m, n, sms, pl))
+        return launch_dense_pair(a, sfa, w, sfw, d, m, n, k, sms, stream);
     CUtensorMap ta, tb;
     GemmParams p{};
     p.kb_total = static_cast<int>(k / 128);

@@ -178,6 +178,27 @@ int fso_gemm_mxfp8_ws_bytes(int64_t m, int64_t n, int64_t k, int64_t* bytes)
     return 0;
 }
 
+int fso_gemm_mxfp8_describe(int64_t m, int64_t n, int64_t k, int64_t sm_count_or_0, int32_t* out6)
+{
+    FSO_REQUIRE(out6 != nullptr, "fso_gemm_mxfp8_describe: out6 is NULL");
+    FSO_REQUIRE(sm_count_or_0 >= 0 && sm_count_or_0 <= 4096, "fso_gemm_mxfp8_describe: sm_count_or_0 = %lld",
+        static_cast<long long>(sm_count_or_0));
+    int const rc = check_gemm_shape("fso_gemm_mxfp8_describe", m, n, k);
+    if (rc != 0) return rc;
+    for (int i = 0; i < 6; ++i) out6[i] = 0;
+    if (m == 0) return 0;
+    int const sms = sm_count_or_0 > 0 ? static_cast<int>(sm_count_or_0) : sm_count();
+    DensePlan const pl = plan_dense(m, n, k, sms);
+    bool const pair = dense_takes_pair(m, n, sms, pl);
+    out6[0] = pl.swap ? 1 : 0;
+    out6[1] = pair ? 256 : pl.bn;
+    out6[2] = pl.splits;
+    out6[3] = pl.kb_per_split;
+    out6[4] = pair ? 1 : 0;
+    out6[5] = pair ? static_cast<int32_t>(((m + 255) / 256) * (n / 256)) : pl.tiles_a * pl.tiles_b;
+    return 0;
+}
+
 int fso_gemm_mxfp8(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
     int64_t k, void* ws, int64_t ws_bytes, void* stream)
 {

@@ -91,6 +91,13 @@ int fso_pack_ue8m0(const void* sf_u8, void* out_sf, int64_t g, int64_t n, int64_
  * Replaces: linear_mxfp8_raw, csrc/gemm/ops/mxfp8.cu:432-541 -> launch_sm100_mxfp8_dispatch (mxfp8.cu:48-51) ->
  * gemm_dispatch_sm100_mxfp8, csrc/gemm/include/blockscale_gemm/arch/sm100/mxfp8/dispatch.cuh:1430-1443. */
 int fso_gemm_mxfp8_ws_bytes(int64_t m, int64_t n, int64_t k, int64_t* bytes);
+/* The route fso_gemm_mxfp8 takes for one shape, as host arithmetic only (no launch, no device needed when
+ * sm_count_or_0 > 0; 0 = the current device's SM count): out6 = { 1 when the weight rows sit on MMA-M (decode-sized
+ * M), MMA-N tile width, K slices, 128-wide K blocks per slice, 1 when the CTA-pair kernel runs it, output tiles }.
+ * The reference decides the same things inside its dispatch cascade and prints them under FSO_PRINT_TILE_INFO
+ * (csrc/gemm/include/blockscale_gemm/arch/sm100/mxfp8/dispatch.cuh:1430-1443, grouped_dispatch.cuh:162-176); it has
+ * no query of its own. */
+int fso_gemm_mxfp8_describe(int64_t m, int64_t n, int64_t k, int64_t sm_count_or_0, int32_t* out6);
 int fso_gemm_mxfp8(const void* a, const void* sfa, const void* w, const void* sfw, void* d, int64_t m, int64_t n,
                    int64_t k, void* ws, int64_t ws_bytes, void* stream);
 

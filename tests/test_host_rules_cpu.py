@@ -71,3 +71,46 @@ def test_eager_calls_run_the_body_and_traced_calls_the_op():
     assert torch.equal(out, x * 2)
     nodes = [n for g in backend.graphs for n in g.graph.nodes if n.op == "call_function"]
     assert len(nodes) == 1 and "fso_test" in str(nodes[0].target)
+
+
+# (M, N, K) on 148 SMs -> (weights on MMA-M, MMA-N tile, K slices, CTA-pair kernel)
+DENSE_ROUTES = [
+    ((8192, 28672, 4096), (False, 256, 1, True)),    # the headline cell: 3584 pair tiles on 74 pairs
+    ((8192, 4096, 14336), (False, 256, 1, True)),
+    ((8192, 3584, 4096), (False, 256, 1, True)),     # the headline cell's eighth (N-split over 8 GPUs)
+    ((1024, 6144, 4096), (False, 128, 1, False)),    # 192 tiles of 256 would leave the second round a third full
+    ((2048, 6144, 4096), (False, 256, 1, True)),     # 192 pair tiles: 3 rounds on 74 pairs against 3 on 148 CTAs
+    ((1024, 4096, 4096), (False, 256, 1, False)),    # 128 tiles fit one round; the pair kernel would need two
+    ((128, 28672, 4096), (False, 256, 1, False)),    # odd number of 128-row blocks: no pairs
+    ((128, 4096, 4096), (False, 128, 4, False)),     # a fifth of a round: narrow tiles and four K slices
+    ((65, 4096, 4096), (False, 128, 4, False)),      # first M past the decode orientation
+    ((64, 4096, 4096), (True, 64, 4, False)),
+    ((32, 6144, 4096), (True, 32, 4, False)),
+    ((16, 28672, 4096), (True, 16, 1, False)),       # 224 weight panels: enough CTAs without slicing K
+    ((16, 4096, 14336), (True, 16, 4, False)),
+    ((1, 4096, 4096), (True, 16, 4, False)),
+]
+
+
+@pytest.mark.parametrize("shape,want", DENSE_ROUTES)
+def test_dense_route_is_a_function_of_the_shape(shape, want, monkeypatch):
+    from fish_scales_ops_b200 import _ops
+
+    got = _ops.gemm_describe(*shape, 148)
+    assert (got["swapped"], got["tile_n"], got["k_slices"], got["pair_kernel"]) == want
+    m, n, k = shape
+    assert got["k_slices"] * got["k_blocks_per_slice"] >= k // 128
+    assert (got["k_slices"] - 1) * got["k_blocks_per_slice"] < k // 128          # no empty slice
+    if not got["swapped"]:
+        rows = 256 if got["pair_kernel"] else 128
+        assert got["tiles"] == -(-m // rows) * -(-n // got["tile_n"])
+
+
+def test_dense_route_refuses_bad_shapes():
+    from fish_scales_ops_b200 import _ops
+
+    with pytest.raises(Exception):
+        _ops.gemm_describe(128, 100, 4096, 148)
+    with pytest.raises(Exception):
+        _ops.gemm_describe(128, 4096, 4096, -1)
+    assert _ops.gemm_describe(0, 4096, 4096, 148)["tiles"] == 0
