@@ -54,6 +54,7 @@ struct GemmParams {
     int num_experts;
     int group_a;               // raster: tiles of A walked together before B advances
     int out_align32;           // the output base is 32-byte aligned (256-bit stores are usable)
+    int stream_b_hint;         // grouped: the weight tiles of an expert with a single block are loaded evict-first
     int64_t out_rows;          // rows of the output (row stride of one split's partial = out_rows * ldo)
     // dense epilogue (kFused kernels and the split-K reduce): out = bf16(act(acc + bias[n]) + residual[m, n])
     const __nv_bfloat16* bias;      // [N] or nullptr
@@ -332,6 +333,17 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 for (int j = 0; j < C::kSfbAtoms; ++j)
                     if (b_row0 + j * 128 < rows_b_pad) ++sfb_atoms;
                 uint32_t const bytes = C::kABytes + C::kBBytes + C::kSfaBytes + 512u * sfb_atoms;
+                // grouped: an expert with one block streams its weight tile exactly once; marking those lines
+                // evict-first leaves L2 to the activation rows (read by every weight tile of the block) and to the
+                // weight tiles a second block of the same expert is about to read again
+                bool stream_b = false;
+                uint64_t pol_first = 0;
+                if constexpr (kGrouped && !kSwap) {
+                    if (p.stream_b_hint != 0 && p.blk0[c.expert + 1] - p.blk0[c.expert] == 1) {
+                        stream_b = true;
+                        pol_first = policy_evict_first();
+                    }
+                }
                 if constexpr (kSwap && !kGrouped) {
                     if (first_tile) {
                         // The weight side of the first stages went out during the CTA's set-up (above); the
@@ -362,7 +374,8 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     uint32_t const fb = full_bar(stage);
                     mbar_expect_tx(fb, bytes);
                     tma_load_2d(sA + stage * C::kABytes, &tm_a, fb, kb * C::kBK, a_row0);
-                    tma_load_2d(sB + stage * C::kBBytes, &tm_b, fb, kb * C::kBK, b_coord);
+                    if (stream_b) tma_load_2d_hint(sB + stage * C::kBBytes, &tm_b, fb, kb * C::kBK, b_coord, pol_first);
+                    else tma_load_2d(sB + stage * C::kBBytes, &tm_b, fb, kb * C::kBK, b_coord);
                     bulk_load(sSfa + stage * C::kSfaBytes,
                         p.sfa + (static_cast<int64_t>(a_row0 / 128) * p.kb_total + kb) * 512, 512, fb);
                     for (int j = 0; j < sfb_atoms; ++j)
