@@ -147,6 +147,16 @@ inline void pick_decode_splits(int64_t tiles, int kb, int limit, int* splits, in
     *kb_per = (kb + best - 1) / best;
 }
 
+// FSO_B200_DENSE_TWO_TOKEN_TILES=0 keeps calls of 65..128 rows in the normal orientation (measurement).
+inline bool two_token_tiles_enabled()
+{
+    static int const v = [] {
+        const char* e = std::getenv("FSO_B200_DENSE_TWO_TOKEN_TILES");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    return v != 0;
+}
+
 inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
 {
     DensePlan p{};
@@ -158,6 +168,20 @@ inline DensePlan plan_dense(int64_t m, int64_t n, int64_t k, int sms)
         p.tiles_b = 1;
         p.group_a = p.tiles_a;
         pick_decode_splits(p.tiles_a, kb, cluster_split_limit(p.bn), &p.splits, &p.kb_per_split);
+    } else if (m <= 128 && n / 128 <= sms && two_token_tiles_enabled()) {
+        // 65..128 rows on a weight of at most one 128-row panel per SM: still a weight-streaming problem. Two 64-row
+        // token tiles per weight panel in the swapped orientation, neighbours in the schedule (the second reads the
+        // panel from L2), K slices summed inside clusters: one launch, where the normal orientation would run a
+        // third of the SMs on 128-wide tiles and sum its K slices through the fp32 workspace in a second launch
+        // (qkv 6144 x 4096 at M = 128: 15.0 us that way, 12.7 us this way, cuBLAS 11.4; o_proj and down alike).
+        p.swap = true;
+        p.bn = 64;
+        p.tiles_a = static_cast<int>(n / 128);
+        p.tiles_b = 2;
+        p.group_a = 1;
+        // (K slices up to 130 / 200 / 296 CTAs measured alike on the Llama shapes: the decode rule's 200 is kept)
+        pick_decode_splits(static_cast<int64_t>(p.tiles_a) * 2, kb, cluster_split_limit(p.bn), &p.splits,
+            &p.kb_per_split);
     } else {
         p.swap = false;
         int const tiles_m = static_cast<int>((m + 127) / 128);
@@ -524,12 +548,13 @@ inline int launch_dense(const void* a, const void* sfa, const void* w, const voi
     int splits = pl.splits;
     bool in_cluster = false;
     if (pl.swap && pl.splits > 1) {
+        int const tiles = pl.tiles_a * pl.tiles_b;
         for (int s2 = pl.splits; s2 >= 2; --s2) {
             int const per = (p.kb_total + s2 - 1) / s2;
             if ((p.kb_total + per - 1) / per != s2) continue;
             // the occupancy query counts one CTA of a cluster per SM; two of these half-SM CTAs share one
-            if (2 * cluster_capacity_bn(pl.bn, s2, fused) >= pl.tiles_a) {
-                if (s2 == pl.splits || pl.tiles_a * s2 * 2 >= sms) {
+            if (2 * cluster_capacity_bn(pl.bn, s2, fused) >= tiles) {
+                if (s2 == pl.splits || tiles * s2 * 2 >= sms) {
                     splits = s2;
                     in_cluster = true;
                 }

@@ -61,8 +61,8 @@ def describe() -> str:
         "format 'bsfp8': a float8_e4m3fn weight with fp32 128x128 block scales is requantized to MXFP8 1x32 by one "
         "fused kernel (value = bf16(fp8 * scale), then the 1x32 rule); a bf16 weight is quantized to MXFP8 directly.",
         "linear(): the 1x32 activation quantizer, then one tcgen05 block-scaled GEMM kernel family (activation rows "
-        "on MMA-M for M > 64, weight rows on MMA-M for M <= 64, split-K with an ordered reduce where the tile count "
-        "leaves SMs idle). bias / residual / activation 'gelu_erf' are applied to the fp32 accumulator before the one "
+        "on MMA-M for large M, weight rows on MMA-M for M <= 64 and for M <= 128 on weights of at most one 128-row "
+        "panel per SM, split-K with an ordered reduce where the tile count leaves SMs idle). bias / residual / activation 'gelu_erf' are applied to the fp32 accumulator before the one "
         "rounding; linear_quantized runs linear (bias, activation) followed by the activation quantizer.",
     ]
     if arch // 10 != SERVED_MAJOR:

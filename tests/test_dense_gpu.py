@@ -34,10 +34,12 @@ def test_config1_single_dense_linear(fso, oracle, device_ok):
 
 
 # (M, N, K): every route of the picker: swapped orientation with 16/32/64-wide token tiles, with and without
-# split-K; normal orientation with 128- and 256-wide tiles, ragged M, split-K, many tiles per CTA.
+# split-K, and with two 64-row token tiles per weight panel (65..128 rows, full and ragged second tile); normal
+# orientation with 128- and 256-wide tiles, ragged M, split-K, many tiles per CTA.
 SHAPES = [(1, 128, 128), (1, 256, 512), (7, 384, 1024), (16, 512, 4096), (17, 256, 512), (32, 1024, 1024),
           (33, 256, 2048), (64, 640, 512), (65, 256, 512), (128, 128, 128), (128, 256, 8192), (200, 384, 640),
-          (256, 512, 256), (300, 1024, 1024), (1024, 4096, 512), (2048, 2560, 384)]
+          (256, 512, 256), (300, 1024, 1024), (1024, 4096, 512), (2048, 2560, 384), (100, 512, 1024),
+          (96, 1024, 2048), (128, 6144, 4096), (127, 4096, 1792), (128, 19200, 256)]
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)

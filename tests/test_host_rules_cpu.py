@@ -82,8 +82,10 @@ DENSE_ROUTES = [
     ((2048, 6144, 4096), (False, 256, 1, True)),     # 192 pair tiles: 3 rounds on 74 pairs against 3 on 148 CTAs
     ((1024, 4096, 4096), (False, 256, 1, False)),    # 128 tiles fit one round; the pair kernel would need two
     ((128, 28672, 4096), (False, 256, 1, False)),    # odd number of 128-row blocks: no pairs
-    ((128, 4096, 4096), (False, 128, 4, False)),     # a fifth of a round: narrow tiles and four K slices
-    ((65, 4096, 4096), (False, 128, 4, False)),      # first M past the decode orientation
+    ((128, 4096, 4096), (True, 64, 3, False)),       # 65..128 rows: two 64-row token tiles per weight panel
+    ((65, 4096, 4096), (True, 64, 3, False)),
+    ((128, 6144, 4096), (True, 64, 2, False)),
+    ((129, 4096, 4096), (False, 128, 2, False)),     # first M in the normal orientation on a small weight
     ((64, 4096, 4096), (True, 64, 4, False)),
     ((32, 6144, 4096), (True, 32, 4, False)),
     ((16, 28672, 4096), (True, 16, 1, False)),       # 224 weight panels: enough CTAs without slicing K
@@ -104,6 +106,8 @@ def test_dense_route_is_a_function_of_the_shape(shape, want, monkeypatch):
     if not got["swapped"]:
         rows = 256 if got["pair_kernel"] else 128
         assert got["tiles"] == -(-m // rows) * -(-n // got["tile_n"])
+    else:
+        assert got["tiles"] == (n // 128) * -(-m // got["tile_n"])
 
 
 def test_dense_route_refuses_bad_shapes():
