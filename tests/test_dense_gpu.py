@@ -275,7 +275,8 @@ def test_cluster_split_k_equals_workspace_split_k(fso, oracle, device_ok):
     from fish_scales_ops_b200 import _ops
 
     shapes = ((16, 4096, 4096), (16, 6144, 4096), (5, 4096, 14336), (16, 512, 4096), (7, 384, 1024),
-              (32, 1024, 1024), (29, 2560, 2048), (64, 512, 1536), (50, 1024, 1536))
+              (32, 1024, 1024), (29, 2560, 2048), (64, 512, 1536), (50, 1024, 1536),
+              (128, 4096, 4096), (100, 1024, 2048), (65, 512, 1536))       # two token tiles per weight panel
     for m, n, k in shapes:
         assert _ops.gemm_ws_bytes(m, n, k) > 0, "pick shapes that take the split-K route"
     cluster = _outputs_in_child_process(shapes, {"FSO_B200_SPLITK": "cluster"}, "splitk_cluster")
