@@ -208,6 +208,51 @@ def timed_e2e(torch, d: Dist, pipe, steps: int, warmup: int = 3, attempts: int =
     return ms, tried
 
 
+def parse_cpulist(text: str):
+    """'0-3,8,10-11' -> {0, 1, 2, 3, 8, 10, 11}."""
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+class NearGpu:
+    """Runs its block on the CPUs next to one GPU's PCIe root (``local_cpulist`` of the device in sysfs), so that the
+    pinned host buffers allocated inside are placed by first touch on that NUMA node; the affinity the process had
+    is put back afterwards (the CPU baseline keeps every core). Best effort: without the sysfs entry, or when the
+    list would not narrow the affinity, nothing changes. ``note`` says what happened."""
+
+    def __init__(self, torch, device_index: int, sysfs: str = "/sys/bus/pci/devices"):
+        self.note, self._cpus, self._old = "host buffers pinned where the process ran (no NUMA information)", None, None
+        try:
+            pr = torch.cuda.get_device_properties(device_index)
+            dev = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            with open(os.path.join(sysfs, dev, "local_cpulist")) as f:
+                text = f.read().strip()
+            old = os.sched_getaffinity(0)
+            near = parse_cpulist(text) & old
+            if near and near != old:
+                self._cpus, self._old = near, old
+                self.note = f"host buffers pinned on the GPU's NUMA node (cpus {text})"
+            elif near:
+                self.note = "host buffers pinned where the process ran (one NUMA node)"
+        except (OSError, ValueError, AttributeError, RuntimeError):
+            pass
+
+    def __enter__(self):
+        if self._cpus:
+            os.sched_setaffinity(0, self._cpus)
+        return self
+
+    def __exit__(self, *exc):
+        if self._old:
+            os.sched_setaffinity(0, self._old)
+        return False
+
+
 class HostPipeline:
     """End-to-end steps with host buffers: every step copies its input from pinned host memory to the device, runs
     ``fn`` on it (the public call) and copies the result back to pinned host memory. The three legs run on three
@@ -356,8 +401,9 @@ def dense_ours(args):
     x_cpu, w_cpu = dense_inputs(torch, m, n, k)
     weight = fso.dense.prepare_weight(w_cpu[r0:r1].cuda(), format="mxfp8")
     x = x_cpu.cuda()
-    x_host = x_cpu.pin_memory()
-    y_host = torch.empty((m, n_local), dtype=torch.bfloat16).pin_memory()
+    with NearGpu(torch, d.local) as near:
+        x_host = x_cpu.pin_memory()
+        y_host = torch.empty((m, n_local), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.current_stream()
 
     def step(ev):
@@ -413,7 +459,8 @@ def dense_ours(args):
         "frac_of_nominal": gemm_tflops / 4500.0, "flops_per_launch": 2.0 * m * n_local * k, "ms_per_launch": gemm_ms}
     line["e2e"] = {"value": flops / (e2e_ms / e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                    "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n_local * 2,
-                   "ms_per_step": e2e_ms / e_steps, "regions_ms_per_step_and_device_allocs": e2e_regions}
+                   "ms_per_step": e2e_ms / e_steps, "regions_ms_per_step_and_device_allocs": e2e_regions,
+                   "host_buffers": near.note}
     line["gpu_launches"] = 2 * args.steps
     line["clocks"] = clocks
     line["device_status"] = status
@@ -595,8 +642,9 @@ def moe_ours(args):
     skew = float(getattr(args, "skew", 0.0) or 0.0)
     hidden_cpu, ids_cpu, w_cpu = moe_inputs(torch, cfg, tokens, 100 + d.rank, skew=skew)
     hidden, ids, wts = hidden_cpu.cuda(), ids_cpu.cuda(), w_cpu.cuda()
-    hidden_host = hidden_cpu.pin_memory()
-    out_host = torch.empty((tokens, cfg["H"]), dtype=torch.bfloat16).pin_memory()
+    with NearGpu(torch, d.local) as near:
+        hidden_host = hidden_cpu.pin_memory()
+        out_host = torch.empty((tokens, cfg["H"]), dtype=torch.bfloat16).pin_memory()
 
     def run(h):
         if d.world == 1:
@@ -677,7 +725,8 @@ def moe_ours(args):
                 f"weight stream {t_mem * 1e3:.3f} ms, tensor {t_cmp * 1e3:.3f} ms"}
     line["e2e"] = {"value": total_tokens / (e2e_ms / e_steps * 1e-3), "unit": "tokens/s",
                    "h2d_bytes_per_step": tokens * cfg["H"] * 2, "d2h_bytes_per_step": tokens * cfg["H"] * 2,
-                   "ms_per_step": e2e_ms / e_steps, "regions_ms_per_step_and_device_allocs": e2e_regions}
+                   "ms_per_step": e2e_ms / e_steps, "regions_ms_per_step_and_device_allocs": e2e_regions,
+                   "host_buffers": near.note}
     # own kernels per step: route (3, or 1 for small batches), gather, FC1, FC2, combine; under expert parallelism
     # also the two plan kernels, the quantizer, the dispatch kernel and the final reduction
     per_step = 7 if tokens * cfg["k"] > 1024 else 5

@@ -118,3 +118,34 @@ def test_dense_route_refuses_bad_shapes():
     with pytest.raises(Exception):
         _ops.gemm_describe(128, 4096, 4096, -1)
     assert _ops.gemm_describe(0, 4096, 4096, 148)["tiles"] == 0
+
+
+def test_host_buffers_are_pinned_next_to_the_gpu(tmp_path, monkeypatch):
+    """bench.py narrows the process affinity to the GPU's local CPUs while it allocates the pinned buffers of the
+    end-to-end leg, and puts the old affinity back."""
+    import os
+    import types
+
+    import bench
+
+    assert bench.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    props = types.SimpleNamespace(pci_domain_id=0, pci_bus_id=0x1B, pci_device_id=0)
+    fake = types.SimpleNamespace(cuda=types.SimpleNamespace(get_device_properties=lambda i: props))
+    dev = tmp_path / "0000:1b:00.0"
+    dev.mkdir()
+    calls = []
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: {0, 1, 2, 3, 4, 5, 6, 7})
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: calls.append(set(cpus)))
+    (dev / "local_cpulist").write_text("4-7,12-15\n")
+    near = bench.NearGpu(fake, 0, sysfs=str(tmp_path))
+    with near:
+        assert calls == [{4, 5, 6, 7}]
+    assert calls == [{4, 5, 6, 7}, {0, 1, 2, 3, 4, 5, 6, 7}] and "NUMA node" in near.note
+    calls.clear()
+    (dev / "local_cpulist").write_text("0-63\n")                  # one node: nothing to narrow
+    with bench.NearGpu(fake, 0, sysfs=str(tmp_path)):
+        pass
+    assert calls == []
+    with bench.NearGpu(fake, 0, sysfs=str(tmp_path / "missing")) as none:      # no sysfs entry: nothing changes
+        pass
+    assert calls == [] and "no NUMA information" in none.note
