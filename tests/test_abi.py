@@ -75,3 +75,49 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(base, f)).read()
                 assert "oracle" not in text.replace("no oracle", ""), os.path.join(base, f)
+
+
+_NOT_PROBED = {"fso_b200_version", "fso_b200_last_error", "fso_stream_fence"}     # no arguments to refuse
+
+
+def test_every_entry_point_refuses_an_all_zero_call(fso):
+    """Zero sizes and NULL pointers everywhere: each entry point answers FSO_ERR_INVALID (-1) with a message of its
+    own before it reaches the device (a positive code would be a CUDA error, i.e. a call that got that far)."""
+    from fish_scales_ops_b200 import _lib
+
+    L = _lib.lib()
+    probed = 0
+    for name, sig in sorted(_lib.SIGNATURES.items()):
+        if name in _NOT_PROBED:
+            continue
+        args = [0 if t in (ctypes.c_int64, ctypes.c_int, ctypes.c_int32) else None for t in sig]
+        assert getattr(L, name)(*args) == -1, name
+        assert _lib.last_error().startswith("fso_"), (name, _lib.last_error())
+        probed += 1
+    assert probed >= 28
+
+
+def test_null_pointers_are_refused_after_the_shape_checks(fso):
+    """Well-formed sizes with NULL operands: refused by the pointer check, still before any launch."""
+    from fish_scales_ops_b200 import _lib
+
+    L = _lib.lib()
+    n = None
+    calls = {
+        "fso_quantize_1x32": (n, n, n, 128, 128, 0, n),
+        "fso_quantize_activation_1x32": (n, n, n, 128, 128, n),
+        "fso_silu_mul_quantize_1x32": (n, n, n, 128, 128, n),
+        "fso_requant_bs128_to_mx": (n, n, n, n, 128, 128, 0, n),
+        "fso_gemm_mxfp8": (n, n, n, n, n, 128, 128, 128, n, 0, n),
+        "fso_gemm_mxfp8_epilogue": (n, n, n, n, n, 128, 128, 128, n, n, 0, n, 0, n),
+        "fso_gemm_mxfp8_quantized": (n, n, n, n, n, n, 128, 128, 128, n, 0, n),
+        "fso_gemm_mxfp8_swiglu": (n, n, n, n, n, n, 128, 256, 128, n),
+        "fso_moe_gather_quant": (n, n, 4, 2, 128, 256, n, n, n),
+        "fso_moe_fc1_swiglu": (n, n, n, n, n, n, 8, 128, 128, 1, 256, n, n, n),
+        "fso_moe_fc2": (n, n, n, n, n, n, 8, 128, 128, 1, 256, n, n),
+        "fso_moe_combine": (n, n, n, n, n, n, 4, 2, 128, n),
+    }
+    for name, args in calls.items():
+        assert len(args) == len(_lib.SIGNATURES[name]), name
+        assert getattr(L, name)(*args) == -1, name
+        assert "NULL" in _lib.last_error(), (name, _lib.last_error())
