@@ -121,3 +121,44 @@ def test_null_pointers_are_refused_after_the_shape_checks(fso):
         assert len(args) == len(_lib.SIGNATURES[name]), name
         assert getattr(L, name)(*args) == -1, name
         assert "NULL" in _lib.last_error(), (name, _lib.last_error())
+
+
+_C_CALLER = r"""
+#include <stdio.h>
+#include <string.h>
+#include "fso_b200.h"
+
+int main(void)
+{
+    fso_moe_plan plan;
+    int32_t route[6];
+    if (fso_b200_version() != 1) return 1;
+    if (fso_moe_plan_make(8192, 2, 8, &plan) != 0 || plan.num_blocks != 135 || plan.rows != 17408) return 2;
+    if (fso_gemm_mxfp8_describe(8192, 28672, 4096, 148, route) != 0) return 3;
+    printf("route %d %d %d %d %d %d\n", route[0], route[1], route[2], route[3], route[4], route[5]);
+    if (fso_gemm_mxfp8(0, 0, 0, 0, 0, 4, 100, 128, 0, 0, 0) != FSO_ERR_INVALID) return 4;
+    if (strstr(fso_b200_last_error(), "multiples of 128") == 0) return 5;
+    printf("ok\n");
+    return 0;
+}
+"""
+
+
+def test_a_c_program_links_the_library_and_calls_it(fso, tmp_path):
+    """The boundary is a C ABI: a C99 translation unit that includes the header links against the library with gcc and
+    calls it (host-only entry points, so this runs without a GPU)."""
+    import shutil
+    import subprocess
+
+    from fish_scales_ops_b200 import _lib
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    src = tmp_path / "caller.c"
+    src.write_text(_C_CALLER)
+    libdir = os.path.dirname(_lib.lib_path())
+    exe = tmp_path / "caller"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-lfso_b200", f"-Wl,-rpath,{libdir}"], check=True, capture_output=True, text=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True, timeout=120).stdout.split("\n")
+    assert out[0] == "route 0 256 1 32 1 3584" and out[1] == "ok"
